@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the fused attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A "step" is one pass of the hot path over one batch of seeded synthetic input.
+The default workload is the causal bf16 prefill forward at B=4, H=32, S=4096,
+D=128 (metric: causal-adjusted attention TFLOP/s); the same run also measures the
+bf16 decode workload (B=64, H=32, D=128, cache 8192, lengths U[1024, 8192]) in
+HBM GB/s and reports it under "decode".  With N > 1 (one process per GPU under
+torchrun) every rank runs the same per-GPU workload on its own batch shard, no
+collective on the data path (weak scaling); the time is the max over ranks.
+
+--impl reference times the reference's own CPU implementation (oracle/_ref, built
+from the unmodified reference sources; else the plain-C oracle) on bounded samples
+of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: dict(kind, dtype, B, Hq, Hkv, L, S, D, causal)
+    "prefill": dict(kind="fwd", dtype="bf16", B=4, Hq=32, Hkv=32, L=4096, S=4096, D=128, causal=True, std=1.0),
+    "gqa": dict(kind="fwd", dtype="f16", B=8, Hq=32, Hkv=8, L=2048, S=2048, D=128, causal=True, std=0.5),
+    "train": dict(kind="fwdbwd", dtype="f16", B=8, Hq=16, Hkv=16, L=2048, S=2048, D=64, causal=True, std=1.0),
+    "cfg1": dict(kind="fwdbwd", dtype="f32", B=2, Hq=4, Hkv=4, L=128, S=128, D=64, causal=True, std=1.0),
+    "decode": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
+}
+ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
+
+
+def fwd_flops(w):
+    """4*B*Hq*L*S*D, halved under the causal mask (L == S)."""
+    f = 4.0 * w["B"] * w["Hq"] * w["L"] * w["S"] * w["D"]
+    return f / 2 if w["causal"] else f
+
+
+def step_flops(w):
+    return fwd_flops(w) * (3.5 if w["kind"] == "fwdbwd" else 1.0)
+
+
+def decode_bytes(w, lens):
+    """K and V rows below each sequence's length, plus q and O."""
+    es = ESIZE[w["dtype"]]
+    return float(int(lens.sum()) * w["Hkv"] * w["D"] * 2 * es + 2 * w["B"] * w["Hq"] * w["D"] * es)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(tflops=float(d["bf16_tflops"]), gbs=float(d["hbm_gbs"]), source="measured (MEASURED_PEAKS.json, burst)")
+    return dict(tflops=1590.0, gbs=6650.0, source="fallback (earlier measurement on this pool)")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])), mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------ CPU side --
+def cpu_reference_runner():
+    """(callable fwd(q,k,v,causal,kv_lens) , callable grad(...), kind, threads usable)."""
+    from oracle.loader import Oracle, Reference
+    if Reference.available():
+        r = Reference()
+        return r, "reference"
+    return Oracle(threads=os.cpu_count() or 1), "port"
+
+
+def cpu_sample(w, runner, kind, n_units, threads, seed=99):
+    """Times `n_units` independent (batch, head) units of workload `w` on the host.
+
+    The reference's CPU path is single-threaded; independent units run on
+    `threads` host threads (the ctypes calls release the GIL).
+    Returns (seconds, work) with work in FLOPs (or bytes for decode).
+    """
+    import concurrent.futures as cf
+    rng = np.random.default_rng(seed)
+    L, S, D = w["L"], w["S"], w["D"]
+    g = w["Hq"] // w["Hkv"]
+    units = []
+    for _ in range(n_units):
+        q = (rng.standard_normal((1, g, L, D), dtype=np.float32) * np.float32(w["std"]))
+        k, v = ((rng.standard_normal((1, 1, S, D), dtype=np.float32) * np.float32(w["std"])) for _ in range(2))
+        units.append((q, k, v))
+    lens = rng.integers(1024, 8193, size=n_units).astype(np.int32) if w["kind"] == "decode" else None
+
+    def one(i):
+        q, k, v = units[i]
+        if kind == "reference":
+            if g > 1:  # the reference's GQA route: repeatInterleave, then attention
+                k, v = runner.repeat_interleave(k, g), runner.repeat_interleave(v, g)
+            if w["kind"] == "decode":
+                runner.fwd(q, k, v, kv_lens=lens[i:i + 1])
+            elif w["kind"] == "fwdbwd":
+                runner.grad(q, k, v, q, causal=w["causal"])
+            else:
+                runner.fwd(q, k, v, causal=w["causal"])
+        else:
+            kw = dict(causal=w["causal"], kv_lens=lens[i:i + 1] if lens is not None else None)
+            runner.fwd(q, k, v, **kw)
+            if w["kind"] == "fwdbwd":
+                runner.bwd(q, k, v, q, **kw)
+
+    if kind == "port":
+        runner.set_threads(1)
+    t0 = time.perf_counter()
+    if threads <= 1:
+        for i in range(n_units):
+            one(i)
+    else:
+        with cf.ThreadPoolExecutor(max_workers=threads) as ex:
+            list(ex.map(one, range(n_units)))
+    dt = time.perf_counter() - t0
+    if w["kind"] == "decode":
+        work = float(int(lens.sum()) * D * 2 * ESIZE[w["dtype"]])
+    else:
+        unit = dict(w, B=1, Hq=g, Hkv=1)
+        work = step_flops(unit) * n_units
+    return dt, work
+
+
+def run_reference_arm(args, w, wname):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    runner, kind = cpu_reference_runner()
+    threads = os.cpu_count() or 1
+    # one step = `threads` units (one per host thread), sized to a few seconds
+    n_units = max(1, min(threads, 32))
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(w, runner, kind, max(1, n_units // 4), threads)
+    tot_t, tot_w = 0.0, 0.0
+    for s in range(args.steps):
+        dt, work = cpu_sample(w, runner, kind, n_units, threads, seed=100 + s)
+        tot_t += dt
+        tot_w += work
+    decode = w["kind"] == "decode"
+    value = tot_w / tot_t / (1e9 if decode else 1e12)
+    unit = "GB/s" if decode else "TFLOP/s"
+    sample = "%d independent (batch, kv-head) units of %s per step (of %d in the full workload)" % (
+        n_units, wname, w["B"] * w["Hkv"])
+    line = {
+        "impl": "reference", "metric": metric_name(w), "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(w, wname),
+        "cpu_baseline": {"value": value, "unit": unit, "cores": min(threads, n_units), "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(w):
+    return "decode HBM GB/s" if w["kind"] == "decode" else "attention TFLOP/s (causal-adj)"
+
+
+def config_of(w, wname):
+    return {"workload": "%s: %s %s B=%d Hq=%d Hkv=%d L=%d S=%d D=%d causal=%s" % (
+        wname, w["kind"], w["dtype"], w["B"], w["Hq"], w["Hkv"], w["L"], w["S"], w["D"], w["causal"]),
+        "l2": "inputs larger than L2 (no flush)" if w["kind"] != "fwdbwd" or w["B"] > 2 else "fits L2",
+        "sharding": "batch x head units per rank, no collective"}
+
+
+# ------------------------------------------------------------------ GPU side --
+def run_ours(args, w, wname):
+    import torch
+    import torch.distributed as dist
+    from tinytorch_b200 import op
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention ops have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[w["dtype"]]
+    peaks = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        """Device time of `steps` calls of fn: CUDA events on the launching stream, max over ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / 1e3
+
+    def build_inputs(wl, seed):
+        g = torch.Generator(device=dev).manual_seed(seed + rank)
+        mk = lambda *s: (torch.randn(s, generator=g, device=dev) * wl["std"]).to(tdt)
+        q = mk(wl["B"], wl["Hq"], wl["L"], wl["D"])
+        k = mk(wl["B"], wl["Hkv"], wl["S"], wl["D"])
+        v = mk(wl["B"], wl["Hkv"], wl["S"], wl["D"])
+        return q, k, v
+
+    def measure(wl, name, steps, warmup, with_e2e):
+        q, k, v = build_inputs(wl, 1234)
+        res = {}
+        if wl["kind"] == "decode":
+            lens_np = np.random.default_rng(1234 + rank).integers(1024, wl["S"] + 1, size=wl["B"]).astype(np.int32)
+            lens = torch.from_numpy(lens_np).to(dev)
+            fn = lambda: op.sdpAttentionDecode(q, k, v, lens)
+            work = decode_bytes(wl, lens_np)
+            launches = 2
+        elif wl["kind"] == "fwdbwd":
+            do = torch.randn_like(q)
+            def fn():
+                o, lse = op.sdpAttentionFwd(q, k, v, isCausal=wl["causal"])
+                op.sdpAttentionBwd(do, q, k, v, o, lse, isCausal=wl["causal"])
+            work = step_flops(wl)
+            launches = 4
+        else:
+            fn = lambda: op.sdpAttentionFwd(q, k, v, isCausal=wl["causal"])
+            work = step_flops(wl)
+            launches = 1
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        sec = timed(fn, steps, warmup)
+        clocks = sampler.stop() if rank == 0 else {}
+        decode = wl["kind"] == "decode"
+        div = 1e9 if decode else 1e12
+        per_gpu = work * steps / sec / div
+        res.update(value=per_gpu * world, ms_per_step=sec / steps * 1e3, clocks=clocks, launches=launches * steps,
+                   per_gpu=per_gpu, work=work)
+        peak = peaks["gbs"] if decode else peaks["tflops"]
+        res["roofline"] = {"bound": "hbm" if decode else "tensor", "achieved": per_gpu, "peak": peak,
+                           "unit": "GB/s" if decode else "TFLOP/s", "frac": per_gpu / peak, "traffic": None,
+                           "peak_source": peaks["source"], "kernel": "decode_kernel" if decode else "fwd_tc_kernel"}
+        if with_e2e:
+            # public API with HOST buffers: pinned inputs -> device, op, result -> pinned host, every step
+            hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+            ho = torch.empty(q.shape, dtype=tdt).pin_memory()
+            dq_, dk_, dv_ = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            def e2e_step():
+                dq_.copy_(hq, non_blocking=True), dk_.copy_(hk, non_blocking=True), dv_.copy_(hv, non_blocking=True)
+                if decode:
+                    o, _ = op.sdpAttentionDecode(dq_, dk_, dv_, lens)
+                else:
+                    o, _ = op.sdpAttentionFwd(dq_, dk_, dv_, isCausal=wl["causal"])
+                ho.copy_(o, non_blocking=True)
+            es = max(2, min(steps, 5))
+            sec2 = timed(e2e_step, es, 1)
+            h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+            res["e2e"] = {"value": work * es / sec2 / div * world, "unit": "GB/s" if decode else "TFLOP/s",
+                          "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": ho.numel() * ho.element_size(),
+                          "ms_per_step": sec2 / es * 1e3}
+        return res
+
+    main = measure(w, wname, args.steps, args.warmup, with_e2e=True)
+    extra = None
+    if wname == "prefill" and not args.no_decode:
+        extra = measure(WORKLOADS["decode"], "decode", max(5, args.steps), max(3, args.warmup), with_e2e=False)
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            runner, kind = cpu_reference_runner()
+            # bounded sample: a few units of the same workload on one core (the reference is single-threaded)
+            n = {"prefill": 6, "gqa": 4, "train": 6, "cfg1": 8, "decode": 16}.get(wname, 4)
+            dt, work = cpu_sample(w, runner, kind, n, 1)
+            dec = w["kind"] == "decode"
+            cpu = {"value": work / dt / (1e9 if dec else 1e12), "unit": "GB/s" if dec else "TFLOP/s", "cores": 1,
+                   "kind": kind, "sample": "%d of %d (batch, kv-head) units of %s, %.1f s" % (
+                       n, w["B"] * w["Hkv"], wname, dt)}
+        decode = w["kind"] == "decode"
+        line = {
+            "metric": metric_name(w), "value": main["value"], "unit": "GB/s" if decode else "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"],
+            "data": "synthetic", "config": config_of(w, wname), "clocks": main["clocks"],
+            "e2e": main.get("e2e"), "gpu_launches": main["launches"], "roofline": main["roofline"],
+            "cpu_baseline": cpu,
+        }
+        if extra:
+            line["decode"] = {"metric": "decode HBM GB/s", "value": extra["value"], "unit": "GB/s",
+                              "ms_per_step": extra["ms_per_step"], "roofline": extra["roofline"],
+                              "config": config_of(WORKLOADS["decode"], "decode"), "clocks": extra["clocks"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w, args.workload)
+    else:
+        run_ours(args, w, args.workload)
+
+
+if __name__ == "__main__":
+    main()

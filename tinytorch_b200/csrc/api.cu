@@ -1,0 +1,215 @@
+// extern "C" entry points of libtt_attn.so: argument validation, workspace
+// handling through the caller's allocator hook, device guard, kernel dispatch.
+// See include/tt_attn.h for the contract of each function.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace ttattn {
+namespace {
+
+thread_local char g_cuda_error[256] = "";
+
+int launch_failed(cudaError_t e) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+  return TT_ATTN_ERR_LAUNCH;
+}
+
+// Equivalent of the reference's CudaDeviceGuard (src/Utils/CUDAUtils.h:100-113).
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    ok = (prev == device) || cudaSetDevice(device) == cudaSuccess;
+    if (prev == device) prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+inline size_t elem_size(int dtype) { return dtype == TT_ATTN_F32 ? 4 : 2; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline bool strides_ok(const Str3& s, size_t es) {
+  return s.b >= 0 && s.h >= 0 && s.s > 0 && (s.b * es) % 16 == 0 && (s.h * es) % 16 == 0 && (s.s * es) % 16 == 0;
+}
+inline size_t round256(size_t n) { return (n + 255) & ~size_t(255); }
+
+// Scratch memory for one call: the caller's buffer, or a block from the hook
+// that is handed back when this object goes out of scope (after the launches
+// have been enqueued; reuse is stream-ordered).
+struct Workspace {
+  void* ptr = nullptr;
+  const tt_attn_alloc_hook* hook = nullptr;
+  int device = 0;
+  bool owned = false;
+  int acquire(size_t need, void* user, size_t user_bytes, const tt_attn_alloc_hook* h, int dev) {
+    if (need == 0) return TT_ATTN_OK;
+    if (user) {
+      if (user_bytes < need) return TT_ATTN_ERR_WORKSPACE;
+      if (!aligned16(user)) return TT_ATTN_ERR_ALIGN;
+      ptr = user;
+      return TT_ATTN_OK;
+    }
+    if (!h || !h->alloc || !h->free) return TT_ATTN_ERR_WORKSPACE;
+    ptr = h->alloc(h->ctx, need, dev);
+    if (!ptr) return TT_ATTN_ERR_WORKSPACE;
+    hook = h, device = dev, owned = true;
+    return TT_ATTN_OK;
+  }
+  ~Workspace() {
+    if (owned) hook->free(hook->ctx, ptr, device);
+  }
+};
+
+int check_common(int dtype, int B, int Hq, int Hkv, int Lq, int Skv, int D) {
+  if (dtype != TT_ATTN_F32 && dtype != TT_ATTN_F16 && dtype != TT_ATTN_BF16) return TT_ATTN_ERR_DTYPE;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Lq <= 0 || Skv <= 0 || Hq % Hkv != 0) return TT_ATTN_ERR_SHAPE;
+  if (D != 64 && D != 128) return TT_ATTN_ERR_HEAD_DIM;
+  if (B > 65535 || Hq > 65535) return TT_ATTN_ERR_TOO_LARGE;  // grid.y / grid.z
+  return TT_ATTN_OK;
+}
+
+}  // namespace
+}  // namespace ttattn
+
+using namespace ttattn;
+
+extern "C" {
+
+int tt_attn_version(void) { return TT_ATTN_ABI_VERSION; }
+
+const char* tt_attn_last_cuda_error(void) { return g_cuda_error; }
+
+const char* tt_attn_strerror(int status) {
+  switch (status) {
+    case TT_ATTN_OK: return "ok";
+    case TT_ATTN_ERR_NULL: return "a required pointer is NULL";
+    case TT_ATTN_ERR_DTYPE: return "unsupported dtype (expected 0=Float32, 1=Float16, 2=BFloat16)";
+    case TT_ATTN_ERR_SHAPE: return "invalid shape";
+    case TT_ATTN_ERR_HEAD_DIM: return "head dimension must be 64 or 128";
+    case TT_ATTN_ERR_ALIGN: return "pointers and strides must be 16-byte aligned";
+    case TT_ATTN_ERR_WORKSPACE: return "workspace too small, or allocator hook missing / returned NULL";
+    case TT_ATTN_ERR_LAUNCH: return "CUDA launch error (see tt_attn_last_cuda_error)";
+    case TT_ATTN_ERR_STRUCT: return "parameter struct size mismatch";
+    case TT_ATTN_ERR_NO_DEVICE: return "invalid device or CUDA driver entry point unavailable";
+    case TT_ATTN_ERR_TOO_LARGE: return "size beyond a fixed limit of this library";
+    default: return "unknown status";
+  }
+}
+
+size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int Lq, int Skv, int D) {
+  (void)dtype;
+  (void)Hkv;
+  if (B <= 0 || Hq <= 0 || D <= 0) return 0;
+  if (kind == TT_ATTN_KIND_BWD) return round256(static_cast<size_t>(B) * Hq * (Lq > 0 ? Lq : 0) * sizeof(float));
+  if (kind == TT_ATTN_KIND_DECODE) {
+    if (Skv <= 0) return 0;
+    int nsplit, chunk;
+    decode_plan(Skv, &nsplit, &chunk);
+    if (nsplit == 1) return 0;
+    return round256(static_cast<size_t>(B) * Hq * nsplit * (D + 2) * sizeof(float));
+  }
+  return 0;
+}
+
+int tt_attn_fwd(const tt_attn_fwd_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_attn_fwd_params)) return TT_ATTN_ERR_STRUCT;
+  if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D)) return rc;
+  if (!p->q || !p->k || !p->v || !p->o) return TT_ATTN_ERR_NULL;
+  const size_t es = elem_size(p->dtype);
+  FwdArgs a{};
+  a.q = p->q, a.k = p->k, a.v = p->v, a.o = p->o, a.lse = p->lse;
+  a.qs = dense_or(p->q_strides, p->Hq, p->Lq, p->D);
+  a.ks = dense_or(p->k_strides, p->Hkv, p->Skv, p->D);
+  a.vs = dense_or(p->v_strides, p->Hkv, p->Skv, p->D);
+  a.os = dense_or(p->o_strides, p->Hq, p->Lq, p->D);
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o) || !strides_ok(a.qs, es) ||
+      !strides_ok(a.ks, es) || !strides_ok(a.vs, es) || !strides_ok(a.os, es))
+    return TT_ATTN_ERR_ALIGN;
+  a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.Lq = p->Lq, a.Skv = p->Skv;
+  a.causal = p->is_causal ? 1 : 0;
+  a.scale = p->scale;
+  a.kv_lens = p->kv_lens;
+  a.status = p->status;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  cudaError_t e = p->dtype == TT_ATTN_F32 ? launch_fwd_simt(p->dtype, p->D, a, stream)
+                                          : launch_fwd_tc(p->dtype, p->D, a, p->device, stream);
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
+int tt_attn_bwd(const tt_attn_bwd_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_attn_bwd_params)) return TT_ATTN_ERR_STRUCT;
+  if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D)) return rc;
+  if (!p->q || !p->k || !p->v || !p->o || !p->d_o || !p->lse) return TT_ATTN_ERR_NULL;
+  if (!p->dq && !p->dk && !p->dv) return TT_ATTN_OK;
+  const size_t es = elem_size(p->dtype);
+  BwdArgs a{};
+  a.q = p->q, a.k = p->k, a.v = p->v, a.o = p->o, a.d_o = p->d_o, a.lse = p->lse;
+  a.dq = p->dq, a.dk = p->dk, a.dv = p->dv;
+  a.qs = dense_or(p->q_strides, p->Hq, p->Lq, p->D);
+  a.ks = dense_or(p->k_strides, p->Hkv, p->Skv, p->D);
+  a.vs = dense_or(p->v_strides, p->Hkv, p->Skv, p->D);
+  a.os = dense_or(p->o_strides, p->Hq, p->Lq, p->D);
+  a.dos = dense_or(p->do_strides, p->Hq, p->Lq, p->D);
+  a.dqs = dense_or(p->dq_strides, p->Hq, p->Lq, p->D);
+  a.dks = dense_or(p->dk_strides, p->Hkv, p->Skv, p->D);
+  a.dvs = dense_or(p->dv_strides, p->Hkv, p->Skv, p->D);
+  const void* ptrs[] = {p->q, p->k, p->v, p->o, p->d_o, p->dq, p->dk, p->dv, p->lse};
+  for (const void* q : ptrs)
+    if (!aligned16(q)) return TT_ATTN_ERR_ALIGN;
+  const Str3* sts[] = {&a.qs, &a.ks, &a.vs, &a.os, &a.dos, &a.dqs, &a.dks, &a.dvs};
+  for (const Str3* s : sts)
+    if (!strides_ok(*s, es)) return TT_ATTN_ERR_ALIGN;
+  a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.Lq = p->Lq, a.Skv = p->Skv;
+  a.causal = p->is_causal ? 1 : 0;
+  a.scale = p->scale;
+  a.kv_lens = p->kv_lens;
+  a.status = p->status;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  Workspace ws;
+  const size_t need = tt_attn_workspace_bytes(TT_ATTN_KIND_BWD, p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D);
+  if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
+  a.delta = static_cast<float*>(ws.ptr);
+  cudaError_t e = launch_bwd_simt(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
+int tt_attn_decode(const tt_attn_decode_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_attn_decode_params)) return TT_ATTN_ERR_STRUCT;
+  if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D)) return rc;
+  if (!p->q || !p->k || !p->v || !p->o) return TT_ATTN_ERR_NULL;
+  const size_t es = elem_size(p->dtype);
+  DecodeArgs a{};
+  a.q = p->q, a.k = p->k, a.v = p->v, a.o = p->o, a.lse = p->lse;
+  a.qs = dense_or(p->q_strides, p->Hq, 1, p->D);
+  a.ks = dense_or(p->k_strides, p->Hkv, p->capacity, p->D);
+  a.vs = dense_or(p->v_strides, p->Hkv, p->capacity, p->D);
+  a.os = dense_or(p->o_strides, p->Hq, 1, p->D);
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o) || !strides_ok(a.qs, es) ||
+      !strides_ok(a.ks, es) || !strides_ok(a.vs, es) || !strides_ok(a.os, es))
+    return TT_ATTN_ERR_ALIGN;
+  a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.capacity = p->capacity;
+  a.scale = p->scale;
+  a.kv_lens = p->kv_lens;
+  decode_plan(p->capacity, &a.nsplit, &a.chunk);
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  Workspace ws;
+  const size_t need =
+      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
+  if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
+  a.partial = static_cast<float*>(ws.ptr);
+  cudaError_t e = launch_decode(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
+}  // extern "C"

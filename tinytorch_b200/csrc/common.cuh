@@ -1,0 +1,113 @@
+// Shared host/device declarations of the attention library's internal launchers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tt_attn.h"
+
+namespace ttattn {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Status bits a kernel may OR into the caller's status word.
+constexpr int kStatusWaitExpired = 1;
+
+struct Str3 {
+  int64_t b, h, s;
+};
+
+inline Str3 dense_or(const tt_attn_strides& st, int64_t H, int64_t S, int64_t D) {
+  if (st.b == 0 && st.h == 0 && st.s == 0) return Str3{H * S * D, S * D, D};
+  return Str3{st.b, st.h, st.s};
+}
+
+// Arguments common to the prefill kernels (SIMT and tensor-core).
+struct FwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;
+  Str3 qs, ks, vs, os;
+  int B, Hq, Hkv, Lq, Skv;
+  int causal;
+  float scale;
+  const int32_t* kv_lens;
+  int32_t* status;
+};
+
+struct BwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;
+  float* delta;  // workspace [B, Hq, Lq]
+  void* dq;
+  void* dk;
+  void* dv;
+  Str3 qs, ks, vs, os, dos, dqs, dks, dvs;
+  int B, Hq, Hkv, Lq, Skv;
+  int causal;
+  float scale;
+  const int32_t* kv_lens;
+  int32_t* status;
+};
+
+struct DecodeArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;
+  float* partial;  // workspace [B, Hq, nsplit, D + 2] when nsplit > 1
+  Str3 qs, ks, vs, os;
+  int B, Hq, Hkv, capacity;
+  int nsplit, chunk;
+  float scale;
+  const int32_t* kv_lens;
+};
+
+// Each returns a cudaError_t from the launch (no synchronisation).
+cudaError_t launch_fwd_tc(int dtype, int D, const FwdArgs& a, int device, cudaStream_t stream);
+cudaError_t launch_fwd_simt(int dtype, int D, const FwdArgs& a, cudaStream_t stream);
+cudaError_t launch_bwd_simt(int dtype, int D, const BwdArgs& a, cudaStream_t stream);
+cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
+
+// Split planning for decode, shared by the launcher and the workspace query.
+void decode_plan(int capacity, int* nsplit, int* chunk);
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) {
+  return x;
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) {
+  return __half2float(x);
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) {
+  return __bfloat162float(x);
+}
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) {
+  return x;
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) {
+  return __float2half_rn(x);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+}  // namespace ttattn

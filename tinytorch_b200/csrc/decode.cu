@@ -1,0 +1,277 @@
+// Single-token decode against a KV cache: a streaming scan bounded by HBM bandwidth.
+//
+// The reference can only express this step as sdpAttention(q[B,H,1,D], Kc, Vc,
+// false, boolmask) (src/Function/FuncNNLayer.h:249-252), which transposes the whole
+// cache (src/Operation/OpTransformCpu.h:54-87) and materialises [B,H,1,S] scores.
+// Here every valid cache byte is read exactly once with 128-bit loads and nothing
+// else of that size touches HBM.
+//
+// Split-KV: CTA (split, kv head, batch) scans keys [split*chunk, (split+1)*chunk)
+// below kv_len[b].  A cache row of D elements is covered by D*sizeof(T)/16 lanes,
+// each holding one 16-byte slice of the row; the lanes of a row reduce the dot
+// product with warp shuffles.  Every lane group keeps an independent online-softmax
+// state (max, sum, D-slice of the weighted V sum) for each of the G query heads
+// that share the kv head, so the loop has no cross-group dependency; states are
+// merged across lane groups (shuffles), warps (shared memory) and, when the
+// sequence was split, by a second small kernel over the per-split partials.
+#include "common.cuh"
+
+namespace ttattn {
+namespace {
+
+constexpr int kThreads = 256, kWarps = 8, UNR = 4;
+
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& w, float (&f)[4]) {
+    f[0] = __uint_as_float(w.x), f[1] = __uint_as_float(w.y), f[2] = __uint_as_float(w.z), f[3] = __uint_as_float(w.w);
+  }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& w, float (&f)[8]) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(u[i] << 16);
+      f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  }
+};
+template <>
+struct Vec16<__half> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& w, float (&f)[8]) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&u[i]));
+      f[2 * i] = t.x, f[2 * i + 1] = t.y;
+    }
+  }
+};
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.cs.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+// G = query heads handled per pass (all share this CTA's kv head).
+template <typename T, int D, int G>
+__global__ void __launch_bounds__(kThreads) decode_kernel(const DecodeArgs a) {
+  constexpr int N = Vec16<T>::N;  // elements per 16-byte slice
+  constexpr int LPK = D / N;      // lanes per cache row
+  constexpr int KPW = 32 / LPK;   // rows per warp-wide load
+  __shared__ float s_acc[kWarps][G][D];
+  __shared__ float s_m[kWarps][G], s_l[kWarps][G];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sub = lane / LPK;        // which of the KPW rows this lane works on
+  const int d0 = (lane % LPK) * N;   // first element of this lane's slice
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = a.Hq / a.Hkv;
+
+  int len = a.capacity;
+  if (a.kv_lens) {
+    int l = a.kv_lens[b];
+    len = l < 0 ? 0 : (l < a.capacity ? l : a.capacity);
+  }
+  const int begin = split * a.chunk;
+  const int end = min(len, begin + a.chunk);
+  const float c = a.scale * kLog2e;
+
+  const T* kbase = reinterpret_cast<const T*>(a.k) + b * a.ks.b + hk * a.ks.h + d0;
+  const T* vbase = reinterpret_cast<const T*>(a.v) + b * a.vs.b + hk * a.vs.h + d0;
+
+  for (int g0 = 0; g0 < group; g0 += G) {
+    const int h0 = hk * group + g0;
+    float qf[G][N];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const T* qp = reinterpret_cast<const T*>(a.q) + b * a.qs.b + (h0 + g) * a.qs.h + d0;
+      Vec16<T>::unpack(*reinterpret_cast<const uint4*>(qp), qf[g]);
+#pragma unroll
+      for (int i = 0; i < N; ++i) qf[g][i] *= c;
+    }
+    float m[G], l[G], acc[G][N];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -INFINITY, l[g] = 0.f;
+#pragma unroll
+      for (int i = 0; i < N; ++i) acc[g][i] = 0.f;
+    }
+
+    // warp w takes rows begin + (it*kWarps + w)*UNR*KPW + u*KPW + sub
+    for (int base = begin + warp * UNR * KPW; base < end; base += kWarps * UNR * KPW) {
+      uint4 kw[UNR], vw[UNR];
+      bool valid[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int row = base + u * KPW + sub;
+        valid[u] = row < end;
+        kw[u] = valid[u] ? ld_stream(kbase + static_cast<int64_t>(row) * a.ks.s) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int row = base + u * KPW + sub;
+        vw[u] = valid[u] ? ld_stream(vbase + static_cast<int64_t>(row) * a.vs.s) : make_uint4(0, 0, 0, 0);
+      }
+      float s[G][UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        float kf[N];
+        Vec16<T>::unpack(kw[u], kf);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float t = 0.f;
+#pragma unroll
+          for (int i = 0; i < N; ++i) t = fmaf(qf[g][i], kf[i], t);
+#pragma unroll
+          for (int o = LPK / 2; o >= 1; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+          s[g][u] = valid[u] ? t : -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float mx = m[g];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) mx = fmaxf(mx, s[g][u]);
+        if (mx == -INFINITY) continue;  // nothing valid for this lane group yet
+        const float alpha = exp2f(m[g] - mx);
+        m[g] = mx;
+        l[g] *= alpha;
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[g][i] *= alpha;
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) s[g][u] = exp2f(s[g][u] - mx);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        float vf[N];
+        Vec16<T>::unpack(vw[u], vf);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float p = (m[g] == -INFINITY) ? 0.f : s[g][u];
+          l[g] += p;
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
+        }
+      }
+    }
+
+    // merge the KPW lane groups of the warp
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m[g], o);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l[g], o);
+        const float mn = fmaxf(m[g], m2);
+        const float w1 = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn);
+        const float w2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
+        l[g] = l[g] * w1 + l2 * w2;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const float a2 = __shfl_xor_sync(0xffffffffu, acc[g][i], o);
+          acc[g][i] = acc[g][i] * w1 + a2 * w2;
+        }
+        m[g] = mn;
+      }
+    }
+    __syncthreads();  // shared arrays free (previous pass consumed)
+    if (sub == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) s_acc[warp][g][d0 + i] = acc[g][i];
+        if (lane == 0) s_m[warp][g] = m[g], s_l[warp][g] = l[g];
+      }
+    }
+    __syncthreads();
+    // merge the warps; thread t handles (head t / D, element t % D)
+    for (int idx = tid; idx < G * D; idx += kThreads) {
+      const int g = idx / D, d = idx % D;
+      float mn = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) mn = fmaxf(mn, s_m[w][g]);
+      float lt = 0.f, at = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float wgt = (s_m[w][g] == -INFINITY) ? 0.f : exp2f(s_m[w][g] - mn);
+        lt += s_l[w][g] * wgt;
+        at += s_acc[w][g][d] * wgt;
+      }
+      const int h = h0 + g;
+      if (a.nsplit == 1) {
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        reinterpret_cast<T*>(a.o)[b * a.os.b + h * a.os.h + d] = from_f32<T>(at * inv);
+        if (a.lse && d == 0) a.lse[static_cast<int64_t>(b) * a.Hq + h] = lt > 0.f ? (mn + log2f(lt)) * kLn2 : -INFINITY;
+      } else {
+        float* pp = a.partial + ((static_cast<int64_t>(b) * a.Hq + h) * a.nsplit + split) * (D + 2);
+        pp[d] = at;
+        if (d == 0) pp[D] = mn, pp[D + 1] = lt;
+      }
+    }
+  }
+}
+
+// One CTA per (head, batch): fold the per-split partials into O and LSE.
+template <typename T, int D>
+__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const float* pp = a.partial + (static_cast<int64_t>(b) * a.Hq + h) * a.nsplit * (D + 2);
+  float mn = -INFINITY;
+  for (int s = 0; s < a.nsplit; ++s) mn = fmaxf(mn, pp[s * (D + 2) + D]);
+  float lt = 0.f, at = 0.f;
+  for (int s = 0; s < a.nsplit; ++s) {
+    const float ms = pp[s * (D + 2) + D];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - mn);
+    lt += pp[s * (D + 2) + D + 1] * w;
+    at += pp[s * (D + 2) + d] * w;
+  }
+  const float inv = lt > 0.f ? 1.f / lt : 0.f;
+  reinterpret_cast<T*>(a.o)[b * a.os.b + h * a.os.h + d] = from_f32<T>(at * inv);
+  if (a.lse && d == 0) a.lse[static_cast<int64_t>(b) * a.Hq + h] = lt > 0.f ? (mn + log2f(lt)) * kLn2 : -INFINITY;
+}
+
+template <typename T, int D>
+cudaError_t launch_t(const DecodeArgs& a, cudaStream_t stream) {
+  const int group = a.Hq / a.Hkv;
+  dim3 grid(a.nsplit, a.Hkv, a.B);
+  if (group % 8 == 0)
+    decode_kernel<T, D, 8><<<grid, kThreads, 0, stream>>>(a);
+  else if (group % 4 == 0)
+    decode_kernel<T, D, 4><<<grid, kThreads, 0, stream>>>(a);
+  else if (group % 2 == 0)
+    decode_kernel<T, D, 2><<<grid, kThreads, 0, stream>>>(a);
+  else
+    decode_kernel<T, D, 1><<<grid, kThreads, 0, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || a.nsplit == 1) return e;
+  decode_combine_kernel<T, D><<<dim3(a.Hq, a.B), D, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+void decode_plan(int capacity, int* nsplit, int* chunk) {
+  // 512-row chunks keep CTAs short enough that mixed sequence lengths balance
+  // across the SMs; at most 64 splits per sequence.
+  int ck = 512;
+  if ((capacity + ck - 1) / ck > 64) ck = (((capacity + 63) / 64) + 63) / 64 * 64;
+  *chunk = ck;
+  *nsplit = capacity <= ck ? 1 : (capacity + ck - 1) / ck;
+}
+
+cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
+  if (dtype == TT_ATTN_F32) return D == 64 ? launch_t<float, 64>(a, stream) : launch_t<float, 128>(a, stream);
+  if (dtype == TT_ATTN_F16) return D == 64 ? launch_t<__half, 64>(a, stream) : launch_t<__half, 128>(a, stream);
+  return D == 64 ? launch_t<__nv_bfloat16, 64>(a, stream) : launch_t<__nv_bfloat16, 128>(a, stream);
+}
+
+}  // namespace ttattn

@@ -1,0 +1,150 @@
+"""Operator layer: the three attention ops a TinyTorch build registers in its
+dispatch tables (reference mechanism: DEFINE_OP / REGISTER_OP_IMPL,
+src/Tensor/Dispatch.h:21-142), here bound to torch tensors used purely as
+device-memory handles.  Every op goes through the C ABI of libtt_attn.so and
+launches on the current CUDA stream of the tensors' device, as reference ops do
+(src/Utils/CUDAUtils.cpp:123-135).  No op has a CPU implementation.
+"""
+import ctypes as C
+import math
+
+import torch
+
+from . import _capi
+
+_DTYPES = {torch.float32: _capi.F32, torch.float16: _capi.F16, torch.bfloat16: _capi.BF16}
+
+
+def _alloc_cb(ctx, nbytes, device):
+    return torch.cuda.caching_allocator_alloc(nbytes, device, torch.cuda.current_stream(device))
+
+
+def _free_cb(ctx, ptr, device):
+    torch.cuda.caching_allocator_delete(ptr)
+
+
+# Workspace hook backed by torch's caching allocator: the stand-in for the
+# reference's getCUDACachedAllocator(device) (src/Tensor/Allocator.cpp:117-139).
+_HOOK = _capi.AllocHook(_capi.ALLOC_FN(_alloc_cb), _capi.FREE_FN(_free_cb), None)
+
+
+def _check_tensor(t, name):
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor (this op has no CPU path)" % name)
+    if t.dim() != 4:
+        raise ValueError("%s must be [B, H, S, D]" % name)
+    if t.stride(3) != 1:
+        raise ValueError("%s: innermost dimension must be contiguous" % name)
+    if t.dtype not in _DTYPES:
+        raise ValueError("%s: dtype %s not supported" % (name, t.dtype))
+
+
+def _strides(t):
+    return _capi.Strides(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _common(p, ref):
+    dev = ref.device.index if ref.device.index is not None else torch.cuda.current_device()
+    p.device = dev
+    p.stream = torch.cuda.current_stream(dev).cuda_stream
+    p.workspace = None
+    p.workspace_bytes = 0
+    p.alloc = C.pointer(_HOOK)
+    p.status = None
+
+
+def default_scale(D):
+    """1/sqrt(D) in fp32, the reference default (src/Function/FuncNNLayer.h:235)."""
+    return 1.0 / math.sqrt(float(D))
+
+
+def sdpAttentionFwd(q, k, v, isCausal=False, scale=None, kvLens=None, needLse=True, status=None):
+    """softmax(scale * Q K^T + bias) V  ->  (O [B,Hq,L,D], LSE [B,Hq,L] fp32 or None)."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_tensor(t, n)
+    if not (q.dtype == k.dtype == v.dtype and q.device == k.device == v.device):
+        raise ValueError("q, k, v must share dtype and device")
+    B, Hq, L, D = q.shape
+    _, Hkv, S, _ = k.shape
+    o = torch.empty((B, Hq, L, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, L), dtype=torch.float32, device=q.device) if needLse else None
+    p = _capi.FwdParams()
+    p.struct_size = C.sizeof(_capi.FwdParams)
+    p.dtype = _DTYPES[q.dtype]
+    p.B, p.Hq, p.Hkv, p.Lq, p.Skv, p.D = B, Hq, Hkv, L, S, D
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides(q), _strides(k), _strides(v), _strides(o)
+    p.is_causal = 1 if isCausal else 0
+    p.scale = default_scale(D) if scale is None else float(scale)
+    p.kv_lens = kvLens.data_ptr() if kvLens is not None else None
+    _common(p, q)
+    if status is not None:
+        p.status = status.data_ptr()
+    _capi.check(_capi.lib().tt_attn_fwd(C.byref(p)))
+    return o, lse
+
+
+def sdpAttentionBwd(dO, q, k, v, o, lse, isCausal=False, scale=None, kvLens=None, needs=(True, True, True)):
+    """Gradients (dQ, dK, dV); entries of `needs` that are False come back as None."""
+    for t, n in ((dO, "dO"), (q, "q"), (k, "k"), (v, "v"), (o, "o")):
+        _check_tensor(t, n)
+    B, Hq, L, D = q.shape
+    _, Hkv, S, _ = k.shape
+    dq = torch.empty_like(q, memory_format=torch.contiguous_format) if needs[0] else None
+    dk = torch.empty_like(k, memory_format=torch.contiguous_format) if needs[1] else None
+    dv = torch.empty_like(v, memory_format=torch.contiguous_format) if needs[2] else None
+    p = _capi.BwdParams()
+    p.struct_size = C.sizeof(_capi.BwdParams)
+    p.dtype = _DTYPES[q.dtype]
+    p.B, p.Hq, p.Hkv, p.Lq, p.Skv, p.D = B, Hq, Hkv, L, S, D
+    p.q, p.k, p.v, p.o, p.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dO.data_ptr()
+    p.lse = lse.data_ptr()
+    p.dq = dq.data_ptr() if dq is not None else None
+    p.dk = dk.data_ptr() if dk is not None else None
+    p.dv = dv.data_ptr() if dv is not None else None
+    p.q_strides, p.k_strides, p.v_strides = _strides(q), _strides(k), _strides(v)
+    p.o_strides, p.do_strides = _strides(o), _strides(dO)
+    if dq is not None:
+        p.dq_strides = _strides(dq)
+    if dk is not None:
+        p.dk_strides = _strides(dk)
+    if dv is not None:
+        p.dv_strides = _strides(dv)
+    p.is_causal = 1 if isCausal else 0
+    p.scale = default_scale(D) if scale is None else float(scale)
+    p.kv_lens = kvLens.data_ptr() if kvLens is not None else None
+    _common(p, q)
+    _capi.check(_capi.lib().tt_attn_bwd(C.byref(p)))
+    return dq, dk, dv
+
+
+def sdpAttentionDecode(q, kCache, vCache, kvLens=None, scale=None, needLse=False, workspace=None):
+    """One query per sequence against a KV cache [B,Hkv,capacity,D] -> (O [B,Hq,1,D], LSE [B,Hq] or None)."""
+    for t, n in ((q, "q"), (kCache, "kCache"), (vCache, "vCache")):
+        _check_tensor(t, n)
+    B, Hq, L, D = q.shape
+    if L != 1:
+        raise ValueError("decode takes exactly one query per sequence")
+    _, Hkv, cap, _ = kCache.shape
+    o = torch.empty((B, Hq, 1, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if needLse else None
+    p = _capi.DecodeParams()
+    p.struct_size = C.sizeof(_capi.DecodeParams)
+    p.dtype = _DTYPES[q.dtype]
+    p.B, p.Hq, p.Hkv, p.capacity, p.D = B, Hq, Hkv, cap, D
+    p.q, p.k, p.v, p.o = q.data_ptr(), kCache.data_ptr(), vCache.data_ptr(), o.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides(q), _strides(kCache), _strides(vCache), _strides(o)
+    p.scale = default_scale(D) if scale is None else float(scale)
+    p.kv_lens = kvLens.data_ptr() if kvLens is not None else None
+    _common(p, q)
+    if workspace is not None:
+        p.workspace = workspace.data_ptr()
+        p.workspace_bytes = workspace.numel() * workspace.element_size()
+    _capi.check(_capi.lib().tt_attn_decode(C.byref(p)))
+    return o, lse
+
+
+def workspaceBytes(kind, dtype, B, Hq, Hkv, Lq, Skv, D):
+    return int(_capi.lib().tt_attn_workspace_bytes(kind, _DTYPES[dtype], B, Hq, Hkv, Lq, Skv, D))

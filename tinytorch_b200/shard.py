@@ -1,0 +1,50 @@
+"""Multi-GPU partitioning of the attention path: contiguous batch x head ranges.
+
+Attention units are independent: one (batch, kv head) pair together with the
+query heads that share it.  Because tensors are dense [B, H, S, D]
+(reference: src/Tensor/TensorImpl.cpp:13-31), a contiguous range of the
+flattened B*Hkv index is one contiguous byte range of Q, K, V and O, so a rank's
+shard is a plain view and no kernel needs a collective.  The only exchange is an
+optional all-gather of O in head-parallel mode, with the semantics of the
+reference's BackendNCCL::allGather (src/Distributed/BackendNCCL.cpp:49-62): rank
+r's block lands at offset r of the gathered buffer.
+"""
+import torch
+import torch.distributed as dist
+
+
+def unit_range(n_units, rank, world):
+    """Contiguous [begin, end) of `n_units` for `rank`; sizes differ by at most one."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank/world")
+    base, rem = divmod(n_units, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def shard_bh(t, n_kv_units, rank, world):
+    """View of the rank's units of a dense [B, H, S, D] tensor as [1, units*g, S, D].
+
+    `n_kv_units` = B * Hkv; H may be Hq (= g * Hkv) or Hkv.
+    """
+    B, H, S, D = t.shape
+    if not t.is_contiguous():
+        raise ValueError("sharding needs the dense layout")
+    g = (B * H) // n_kv_units
+    b0, b1 = unit_range(n_kv_units, rank, world)
+    return t.view(B * H, S, D)[b0 * g:b1 * g].unsqueeze(0)
+
+
+def all_gather_output(o_local, n_kv_units, world, group=None):
+    """Gather per-rank O shards ([1, units_r*g, L, D]) into [sum units*g, L, D].
+
+    Uses all_gather on equal-sized padded blocks when shard sizes differ.
+    """
+    sizes = [unit_range(n_kv_units, r, world) for r in range(world)]
+    g = o_local.shape[1] // max(1, sizes[dist.get_rank(group)][1] - sizes[dist.get_rank(group)][0])
+    mx = max(e - b for b, e in sizes) * g
+    pad = torch.zeros((mx,) + tuple(o_local.shape[2:]), dtype=o_local.dtype, device=o_local.device)
+    pad[:o_local.shape[1]] = o_local[0]
+    outs = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(outs, pad, group=group)
+    return torch.cat([outs[r][:(e - b) * g] for r, (b, e) in enumerate(sizes)], dim=0)
