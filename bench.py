@@ -36,6 +36,9 @@ WORKLOADS = {
     "train": dict(kind="fwdbwd", dtype="f16", B=8, Hq=16, Hkv=16, L=2048, S=2048, D=64, causal=True, std=1.0),
     "cfg1": dict(kind="fwdbwd", dtype="f32", B=2, Hq=4, Hkv=4, L=128, S=128, D=64, causal=True, std=1.0),
     "decode": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
+    # reduced copies of the two headline workloads, sized for an ncu capture (inputs still larger than L2)
+    "prefill_ncu": dict(kind="fwd", dtype="bf16", B=2, Hq=32, Hkv=32, L=4096, S=4096, D=128, causal=True, std=1.0),
+    "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
 
@@ -305,24 +308,36 @@ def run_ours(args, w, wname):
         peak = peaks["gbs"] if decode else peaks["tflops"]
         res["roofline"] = {"bound": "hbm" if decode else "tensor", "achieved": per_gpu, "peak": peak,
                            "unit": "GB/s" if decode else "TFLOP/s", "frac": per_gpu / peak, "traffic": None,
-                           "peak_source": peaks["source"], "kernel": "decode_kernel" if decode else "fwd_tc_kernel"}
+                           "peak_source": peaks["source"],
+                           "kernel": "decode_kernel" if decode else ("fwd_simt_kernel" if wl["dtype"] == "f32" else "fwd_tc_kernel")}
         if with_e2e:
             # public API with HOST buffers: pinned inputs -> device, op, result -> pinned host, every step
             hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
             ho = torch.empty(q.shape, dtype=tdt).pin_memory()
             dq_, dk_, dv_ = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            train = wl["kind"] == "fwdbwd"
+            if train:
+                hdo = do.cpu().pin_memory()
+                ddo_ = torch.empty_like(q)
+                hg = [torch.empty(t.shape, dtype=tdt).pin_memory() for t in (q, k, v)]
             def e2e_step():
                 dq_.copy_(hq, non_blocking=True), dk_.copy_(hk, non_blocking=True), dv_.copy_(hv, non_blocking=True)
                 if decode:
                     o, _ = op.sdpAttentionDecode(dq_, dk_, dv_, lens)
+                elif train:
+                    ddo_.copy_(hdo, non_blocking=True)
+                    o, lse = op.sdpAttentionFwd(dq_, dk_, dv_, isCausal=wl["causal"])
+                    for h_, g_ in zip(hg, op.sdpAttentionBwd(ddo_, dq_, dk_, dv_, o, lse, isCausal=wl["causal"])):
+                        h_.copy_(g_, non_blocking=True)
                 else:
                     o, _ = op.sdpAttentionFwd(dq_, dk_, dv_, isCausal=wl["causal"])
                 ho.copy_(o, non_blocking=True)
             es = max(2, min(steps, 5))
             sec2 = timed(e2e_step, es, 1)
-            h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+            h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hdo) if train else (hq, hk, hv)))
+            d2h = ho.numel() * ho.element_size() + (sum(t.numel() * t.element_size() for t in hg) if train else 0)
             res["e2e"] = {"value": work * es / sec2 / div * world, "unit": "GB/s" if decode else "TFLOP/s",
-                          "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": ho.numel() * ho.element_size(),
+                          "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                           "ms_per_step": sec2 / es * 1e3}
         return res
 
@@ -336,7 +351,7 @@ def run_ours(args, w, wname):
         if world == 1 and not args.no_cpu:
             runner, kind = cpu_reference_runner()
             # bounded sample: a few units of the same workload on one core (the reference is single-threaded)
-            n = {"prefill": 6, "gqa": 4, "train": 6, "cfg1": 8, "decode": 16}.get(wname, 4)
+            n = {"prefill": 6, "gqa": 4, "train": 6, "cfg1": 8, "decode": 16, "decode_ncu": 16}.get(wname, 4)
             dt, work = cpu_sample(w, runner, kind, n, 1)
             dec = w["kind"] == "decode"
             cpu = {"value": work / dt / (1e9 if dec else 1e12), "unit": "GB/s" if dec else "TFLOP/s", "cores": 1,
