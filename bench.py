@@ -341,7 +341,7 @@ def run_ours(args, w, wname):
                           "ms_per_step": sec2 / es * 1e3}
         return res
 
-    main = measure(w, wname, args.steps, args.warmup, with_e2e=True)
+    main = measure(w, wname, args.steps, args.warmup, with_e2e=not args.no_e2e)
     extra = None
     if wname == "prefill" and not args.no_decode:
         extra = measure(WORKLOADS["decode"], "decode", max(5, args.steps), max(3, args.warmup), with_e2e=False)
@@ -384,6 +384,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

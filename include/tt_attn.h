@@ -178,6 +178,27 @@ TT_ATTN_API int tt_attn_fwd(const tt_attn_fwd_params* p);
 TT_ATTN_API int tt_attn_bwd(const tt_attn_bwd_params* p);
 TT_ATTN_API int tt_attn_decode(const tt_attn_decode_params* p);
 
+/* Decode for callers that cannot give this library any device memory: hosts
+ * where an embedding runtime owns the whole device heap and offers neither an
+ * allocator callback nor a spare buffer, and token loops that must not touch an
+ * allocator at all (cudaMalloc takes a process-wide lock and may synchronise the
+ * device).  Same arguments and result as tt_attn_decode, but `workspace`,
+ * `workspace_bytes` and `alloc` are ignored and neither this call nor anything
+ * it uses allocates or frees memory: the per-split partial results go to a fixed
+ * TT_ATTN_STATIC_SCRATCH_BYTES array inside the library image (resident on every
+ * GPU that loads the library, until the process exits).
+ *  - A problem whose tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, ...) exceeds
+ *    TT_ATTN_STATIC_SCRATCH_BYTES is refused with TT_ATTN_ERR_TOO_LARGE.
+ *  - The first call on each device looks up the array's device address (once,
+ *    with that device current); make that first call before starting any stream
+ *    capture.
+ *  - All calls on a device share the one array, which is never cleared (no part
+ *    of it needs to start at zero); calls that overlap in time on the same GPU
+ *    race on it, so keep them on one stream or otherwise ordered.
+ * This entry point has no counterpart in the reference. */
+#define TT_ATTN_STATIC_SCRATCH_BYTES (24u << 20)
+TT_ATTN_API int tt_attn_decode_static(const tt_attn_decode_params* p);
+
 /* Scratch bytes the given call needs (0 if none).  Skv is the cache capacity
  * for TT_ATTN_KIND_DECODE. */
 TT_ATTN_API size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int Lq, int Skv, int D);

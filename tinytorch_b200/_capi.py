@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libtt_attn.so")
 
 F32, F16, BF16 = 0, 1, 2
 KIND_FWD, KIND_BWD, KIND_DECODE = 0, 1, 2
+STATIC_SCRATCH_BYTES = 24 << 20  # TT_ATTN_STATIC_SCRATCH_BYTES
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_size_t, C.c_int)
 FREE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int)
@@ -70,7 +71,7 @@ class DecodeParams(C.Structure):
     ]
 
 
-EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_workspace_bytes", "tt_attn_strerror",
+EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_static", "tt_attn_workspace_bytes", "tt_attn_strerror",
            "tt_attn_last_cuda_error", "tt_attn_version")
 
 _lib = None
@@ -94,6 +95,8 @@ def lib():
         L.tt_attn_fwd.argtypes = [C.POINTER(FwdParams)]
         L.tt_attn_bwd.argtypes = [C.POINTER(BwdParams)]
         L.tt_attn_decode.argtypes = [C.POINTER(DecodeParams)]
+        L.tt_attn_decode_static.argtypes = [C.POINTER(DecodeParams)]
+        L.tt_attn_decode_static.restype = C.c_int
         for n in ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_version"):
             getattr(L, n).restype = C.c_int
         L.tt_attn_workspace_bytes.argtypes = [C.c_int] * 8

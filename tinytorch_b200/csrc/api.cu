@@ -212,4 +212,35 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
 
+int tt_attn_decode_static(const tt_attn_decode_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_attn_decode_params)) return TT_ATTN_ERR_STRUCT;
+  if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D)) return rc;
+  if (!p->q || !p->k || !p->v || !p->o) return TT_ATTN_ERR_NULL;
+  const size_t es = elem_size(p->dtype);
+  DecodeArgs a{};
+  a.q = p->q, a.k = p->k, a.v = p->v, a.o = p->o, a.lse = p->lse;
+  a.qs = dense_or(p->q_strides, p->Hq, 1, p->D);
+  a.ks = dense_or(p->k_strides, p->Hkv, p->capacity, p->D);
+  a.vs = dense_or(p->v_strides, p->Hkv, p->capacity, p->D);
+  a.os = dense_or(p->o_strides, p->Hq, 1, p->D);
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o) || !strides_ok(a.qs, es) ||
+      !strides_ok(a.ks, es) || !strides_ok(a.vs, es) || !strides_ok(a.os, es))
+    return TT_ATTN_ERR_ALIGN;
+  a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.capacity = p->capacity;
+  a.scale = p->scale;
+  a.kv_lens = p->kv_lens;
+  decode_plan(p->capacity, &a.nsplit, &a.chunk);
+  const size_t need =
+      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
+  if (need > TT_ATTN_STATIC_SCRATCH_BYTES) return TT_ATTN_ERR_TOO_LARGE;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  bool too_large = false;
+  cudaError_t e =
+      launch_decode_static(p->dtype, p->D, a, need, p->device, static_cast<cudaStream_t>(p->stream), &too_large);
+  if (too_large) return TT_ATTN_ERR_TOO_LARGE;
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
 }  // extern "C"

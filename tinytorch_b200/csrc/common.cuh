@@ -78,6 +78,9 @@ cudaError_t launch_fwd_simt(int dtype, int D, const FwdArgs& a, cudaStream_t str
 cudaError_t launch_bwd_simt(int dtype, int D, const BwdArgs& a, cudaStream_t stream);
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
 
+cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, int device, cudaStream_t stream,
+                                 bool* too_large);
+
 // Split planning for decode, shared by the launcher and the workspace query.
 void decode_plan(int capacity, int* nsplit, int* chunk);
 

@@ -14,6 +14,8 @@
 // that share the kv head, so the loop has no cross-group dependency; states are
 // merged across lane groups (shuffles), warps (shared memory) and, when the
 // sequence was split, by a second small kernel over the per-split partials.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ttattn {
@@ -272,6 +274,53 @@ cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t st
   if (dtype == TT_ATTN_F32) return D == 64 ? launch_t<float, 64>(a, stream) : launch_t<float, 128>(a, stream);
   if (dtype == TT_ATTN_F16) return D == 64 ? launch_t<__half, 64>(a, stream) : launch_t<__half, 128>(a, stream);
   return D == 64 ? launch_t<__nv_bfloat16, 64>(a, stream) : launch_t<__nv_bfloat16, 128>(a, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free decode.  Some hosts may launch kernels but have no way to hand
+// this library device memory: an embedding runtime that owns the whole heap and
+// exposes neither an allocator callback nor a spare buffer, or a serving loop
+// whose latency budget rules out allocator calls on the token path (cudaMalloc
+// takes a process-wide lock and may synchronise the device).  For them the
+// per-split partials live in a fixed array inside the library image instead of in
+// caller-provided scratch.  Every GPU that loads the library carries the array
+// until the process exits, hence the modest size.
+//
+// The array is shared by every call on a device and keeps the previous call's
+// contents.  Nothing in it has to start at zero: each launch writes every
+// (batch, head, split) slot before the combine kernel reads it.  Two calls that
+// overlap on the GPU (different streams) would race on it.
+namespace {
+
+constexpr size_t kStaticScratchBytes = TT_ATTN_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices] = {};
+
+}  // namespace
+
+// `device` must be the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use, so the device address
+// is looked up once per device with cudaGetSymbolAddress and cached.
+cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, int device, cudaStream_t stream,
+                                 bool* too_large) {
+  *too_large = need > kStaticScratchBytes || device < 0 || device >= kMaxDevices;
+  if (*too_large) return cudaSuccess;
+  void* ptr = nullptr;
+  if (need > 0) {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ptr[device]) {
+      void* sym = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&sym, g_decode_scratch);
+      if (e != cudaSuccess) return e;
+      g_scratch_ptr[device] = sym;
+    }
+    ptr = g_scratch_ptr[device];
+  }
+  a.partial = static_cast<float*>(ptr);
+  return launch_decode(dtype, D, a, stream);
 }
 
 }  // namespace ttattn
