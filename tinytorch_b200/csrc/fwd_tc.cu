@@ -4,22 +4,24 @@
 // (reference: src/Function/FuncNNLayer.h:231-266) by one fused kernel that never
 // writes the [L,S] score matrix to HBM.
 //
-// One CTA owns a 128-row query tile of one (batch, head) and walks the key/value
-// sequence in 128-row tiles:
-//   warp 4   producer : TMA tiled loads (128-byte swizzle, no multicast) of the Q
-//                       tile once and of each K and V tile into shared memory
-//   warp 5   issuer   : one thread issues tcgen05.mma; S = Q.K^T accumulates in
-//                       TMEM columns [0,128), O += P.V in TMEM columns [128,128+D)
-//   warps 0-3 softmax : thread t owns query row t (= TMEM lane t): reads its S
-//                       row with tcgen05.ld, keeps the running max / sum in
-//                       registers (no cross-thread reduction is needed in this
-//                       layout), writes P as packed 16-bit pairs over the S
-//                       columns with tcgen05.st, rescales O only when the row
-//                       max grew by more than 2^8, and finally writes O and LSE
+// One CTA owns two 128-row query tiles of one (batch, head) and walks the
+// key/value sequence in 128-row tiles (1 CTA per SM, all 512 TMEM columns):
+//   warp 8   producer : TMA tiled loads (128-byte swizzle, no multicast) of both Q
+//                       tiles once and of each K and V tile into a 2-stage ring
+//   warp 9   issuer   : one thread issues tcgen05.mma; S_t = Q_t.K^T accumulates in
+//                       TMEM columns [t*128, t*128+128), O_t += P_t.V in columns
+//                       [256 + t*D, 256 + (t+1)*D).  The two tiles are interleaved
+//                       so that the tensor pipe computes for one tile while the
+//                       other tile's warpgroup is in its softmax.
+//   warps 0-3 / 4-7   : softmax warpgroup of tile 0 / 1.  Thread r owns query row r
+//                       (= TMEM lane r): it reads the whole 128-column S row with
+//                       tcgen05.ld, so the row max and row sum need no cross-thread
+//                       reduction in this layout; exponentials run as packed fp32
+//                       pairs (fma.rn.f32x2 + ex2); P is written as packed 16-bit
+//                       pairs over the S columns with tcgen05.st; O is rescaled
+//                       only when the row max grew by more than 2^8; the same
+//                       warpgroup finally writes O and LSE.
 // P never leaves TMEM: the second MMA takes its A operand from TMEM.
-// K and V are single-buffered so that two CTAs fit on one SM (96 KB + 256 TMEM
-// columns each); the second CTA's MMAs fill the tensor pipe while the first is in
-// its softmax.
 #include <cuda.h>
 
 #include <mutex>
@@ -31,14 +33,18 @@
 namespace ttattn {
 namespace {
 
-constexpr int BM = 128;  // query rows per CTA
-constexpr int BN = 128;  // keys per tile
-constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
+constexpr int BM = 128;      // rows of one query tile (= TMEM lanes)
+constexpr int QT = 2;        // query tiles per CTA
+constexpr int BN = 128;      // keys per tile
+constexpr int NSTAGE = 2;    // K/V ring depth
+constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the producer and issuer warps
+constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct __align__(8) SmemCtl {
-  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint64_t q_full;
+  uint64_t k_full[NSTAGE], k_empty[NSTAGE], v_full[NSTAGE], v_empty[NSTAGE];
+  uint64_t s_full[QT], p_full[QT], o_full[QT];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -47,11 +53,9 @@ template <int D>
 constexpr int tile_bytes() {
   return BM * D * 2;
 }
-// Sized for D = 128 at every D: the request also caps residency at two CTAs
-// per SM, which is what the 512 TMEM columns allow (256 per CTA).
 template <int D>
 constexpr int smem_bytes() {
-  return 3 * tile_bytes<128>() + 1024 /*alignment slack*/ + 128 /*SmemCtl*/;
+  return (QT + 2 * NSTAGE) * tile_bytes<D>() + 1024 /*alignment slack*/ + 256 /*SmemCtl*/;
 }
 
 template <bool BF16>
@@ -66,53 +70,66 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 template <int D, bool BF16>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
     fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + tile_bytes<D>();
-  uint8_t* sV = smem + 2 * tile_bytes<D>();
-  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + 3 * tile_bytes<D>());
+  constexpr int TB = tile_bytes<D>();
+  uint8_t* sQ = smem;                    // QT tiles
+  uint8_t* sK = smem + QT * TB;          // NSTAGE tiles
+  uint8_t* sV = sK + NSTAGE * TB;        // NSTAGE tiles
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(sV + NSTAGE * TB);
   volatile int* abort_flag = &ctl->abort_flag;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   // Heaviest (latest) causal tiles are launched first.
-  const int mt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int mp = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hkv);
-  const int row0 = mt * BM;
+  const int row0 = mp * (QT * BM);
 
   int kv_len = a.Skv;
   if (a.kv_lens) {
     int l = a.kv_lens[b];
     kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
   }
-  int kv_end = kv_len;
-  if (a.causal && row0 + BM < kv_end) kv_end = row0 + BM;
-  const int n_tiles = (kv_end + BN - 1) / BN;
+  // Number of key tiles each query tile walks (0 for a tile wholly beyond Lq).
+  auto tiles_of = [&](int t) {
+    int kv_end = kv_len;
+    if (a.causal && row0 + t * BM + BM < kv_end) kv_end = row0 + t * BM + BM;
+    return (row0 + t * BM < a.Lq) ? (kv_end + BN - 1) / BN : 0;
+  };
+  const int nt0 = tiles_of(0), nt1 = tiles_of(1);
+  const int n_max = nt0 > nt1 ? nt0 : nt1;
+  auto nt = [&](int t) { return t == 0 ? nt0 : nt1; };
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     ptx::mbar_init(&ctl->q_full, 1);
-    ptx::mbar_init(&ctl->k_full, 1);
-    ptx::mbar_init(&ctl->k_empty, 1);
-    ptx::mbar_init(&ctl->v_full, 1);
-    ptx::mbar_init(&ctl->v_empty, 1);
-    ptx::mbar_init(&ctl->s_full, 1);
-    ptx::mbar_init(&ctl->p_full, 128);
-    ptx::mbar_init(&ctl->o_full, 1);
+#pragma unroll
+    for (int i = 0; i < NSTAGE; ++i) {
+      ptx::mbar_init(&ctl->k_full[i], 1);
+      ptx::mbar_init(&ctl->k_empty[i], 1);
+      ptx::mbar_init(&ctl->v_full[i], 1);
+      ptx::mbar_init(&ctl->v_empty[i], 1);
+    }
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+      ptx::mbar_init(&ctl->s_full[t], 1);
+      ptx::mbar_init(&ctl->p_full[t], BM);
+      ptx::mbar_init(&ctl->o_full[t], 1);
+    }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);
     ptx::tma_prefetch_desc(&tmK);
     ptx::tma_prefetch_desc(&tmV);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -120,38 +137,46 @@ __global__ void __launch_bounds__(kThreads, 2)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tS = tmem;        // S (fp32, 128 cols); P (16-bit pairs) overlays cols [0,64)
-  const uint32_t tO = tmem + 128;  // O (fp32, D cols)
+  // TMEM columns: S_t (fp32, 128) at t*128, P_t (16-bit pairs) overlays S_t[0,64); O_t (fp32, D) at 256 + t*D.
 
   constexpr int HALVES = D / 64;  // 64-element (128-byte) column blocks per row
   constexpr int HALF_BYTES = BM * 128;
 
-  if (warp == 4) {
+  // Register budget: the softmax warpgroups hold a whole 128-column S row per
+  // thread; the producer / issuer warpgroup needs almost nothing.
+  if (warp >= 8) {
+    ptx::setmaxnreg_dec<72>();
+  if (warp == 8) {
     // ------------------------------------------------------------ producer --
-    if (lane == 0 && n_tiles > 0) {
-      ptx::mbar_arrive_expect_tx(&ctl->q_full, tile_bytes<D>());
+    if (lane == 0 && n_max > 0) {
+      ptx::mbar_arrive_expect_tx(&ctl->q_full, QT * TB);
 #pragma unroll
-      for (int hf = 0; hf < HALVES; ++hf) ptx::tma_load_4d(sQ + hf * HALF_BYTES, &tmQ, &ctl->q_full, hf * 64, row0, h, b);
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t ph = static_cast<uint32_t>(j & 1);
-        ok = ptx::mbar_wait(&ctl->k_empty, ph ^ 1, abort_flag);
-        if (!ok) break;
-        ptx::mbar_arrive_expect_tx(&ctl->k_full, tile_bytes<D>());
+      for (int t = 0; t < QT; ++t)
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf)
-          ptx::tma_load_4d(sK + hf * HALF_BYTES, &tmK, &ctl->k_full, hf * 64, j * BN, hk, b);
-        ok = ptx::mbar_wait(&ctl->v_empty, ph ^ 1, abort_flag);
-        if (!ok) break;
-        ptx::mbar_arrive_expect_tx(&ctl->v_full, tile_bytes<D>());
+          ptx::tma_load_4d(sQ + t * TB + hf * HALF_BYTES, &tmQ, &ctl->q_full, hf * 64, row0 + t * BM, h, b);
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % NSTAGE;
+        const uint32_t ph = static_cast<uint32_t>((j / NSTAGE) & 1);
+        if (!ptx::mbar_wait(&ctl->k_empty[st], ph ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(&ctl->k_full[st], TB);
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf)
-          ptx::tma_load_4d(sV + hf * HALF_BYTES, &tmV, &ctl->v_full, hf * 64, j * BN, hk, b);
+          ptx::tma_load_4d(sK + st * TB + hf * HALF_BYTES, &tmK, &ctl->k_full[st], hf * 64, j * BN, hk, b);
+        if (!ptx::mbar_wait(&ctl->v_empty[st], ph ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(&ctl->v_full[st], TB);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf)
+          ptx::tma_load_4d(sV + st * TB + hf * HALF_BYTES, &tmV, &ctl->v_full[st], hf * 64, j * BN, hk, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // -------------------------------------------------------------- issuer --
-    if (lane == 0 && n_tiles > 0) {
+    // Order per key tile j:  PV(0,j)  QK(0,j+1)  PV(1,j)  QK(1,j+1): while one
+    // warpgroup is in its softmax the tensor pipe works for the other.  MMAs of
+    // one thread execute in issue order, so QK(t,j+1) overwriting S_t / P_t
+    // cannot pass PV(t,j) that still reads P_t.
+    if (lane == 0 && n_max > 0) {
       // A negative scale is folded into the sign of Q so that the softmax
       // always works with a non-negative multiplier.
       const uint32_t neg = a.scale < 0.f ? (1u << 13) : 0u;
@@ -159,72 +184,103 @@ __global__ void __launch_bounds__(kThreads, 2)
       const uint32_t idesc_pv = ptx::make_idesc_f16(BM, D, BF16 ? 1 : 0, 0, 1);
       const uint32_t aQ = ptx::smem_u32(sQ), aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV);
       bool ok = ptx::mbar_wait(&ctl->q_full, 0, abort_flag);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t ph = static_cast<uint32_t>(j & 1);
-        ok = ptx::mbar_wait(&ctl->k_full, ph, abort_flag);
-        if (!ok) break;
+
+      auto issue_qk = [&](int t, int j) -> bool {
+        const int st = j % NSTAGE;
+        if (!ptx::mbar_wait(&ctl->k_full[st], static_cast<uint32_t>((j / NSTAGE) & 1), abort_flag)) return false;
         ptx::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           // K-major operands: 64-element halves 16 KB apart, 32 bytes per k-step
           const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          ptx::mma_ss(tS, ptx::make_smem_desc_sw128(aQ + off, 16, 1024), ptx::make_smem_desc_sw128(aK + off, 16, 1024),
-                      idesc_qk, ks > 0 ? 1u : 0u);
+          ptx::mma_ss(tmem + t * 128, ptx::make_smem_desc_sw128(aQ + t * TB + off, 16, 1024),
+                      ptx::make_smem_desc_sw128(aK + st * TB + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
         }
-        ptx::mma_commit(&ctl->k_empty);
-        ptx::mma_commit(&ctl->s_full);
-        ok = ptx::mbar_wait(&ctl->v_full, ph, abort_flag);
-        if (!ok) break;
-        ok = ptx::mbar_wait(&ctl->p_full, ph, abort_flag);
-        if (!ok) break;
+        ptx::mma_commit(&ctl->s_full[t]);
+        return true;
+      };
+      auto issue_pv = [&](int t, int j) -> bool {
+        const int st = j % NSTAGE;
+        if (!ptx::mbar_wait(&ctl->v_full[st], static_cast<uint32_t>((j / NSTAGE) & 1), abort_flag)) return false;
+        if (!ptx::mbar_wait(&ctl->p_full[t], static_cast<uint32_t>(j & 1), abort_flag)) return false;
         ptx::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           // V is N(=D)-contiguous: 16 keys per k-step = 2048 bytes; the two
           // 64-wide column blocks of D=128 are HALF_BYTES apart (LBO).
-          ptx::mma_ts(tO, tS + ks * 8, ptx::make_smem_desc_sw128(aV + ks * 2048, HALF_BYTES, 1024), idesc_pv,
+          ptx::mma_ts(tmem + 256 + t * D, tmem + t * 128 + ks * 8,
+                      ptx::make_smem_desc_sw128(aV + st * TB + ks * 2048, HALF_BYTES, 1024), idesc_pv,
                       (j > 0 || ks > 0) ? 1u : 0u);
         }
-        ptx::mma_commit(&ctl->v_empty);
-        if (j == n_tiles - 1) ptx::mma_commit(&ctl->o_full);
+        return true;
+      };
+
+#pragma unroll
+      for (int t = 0; t < QT && ok; ++t)
+        if (nt(t) > 0) ok = issue_qk(t, 0);
+      if (ok) ptx::mma_commit(&ctl->k_empty[0]);
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int last_pv = (j < nt1) ? 1 : 0;
+        const int last_qk = (j + 1 < nt1) ? 1 : 0;
+#pragma unroll
+        for (int t = 0; t < QT && ok; ++t) {
+          if (j < nt(t)) {
+            ok = issue_pv(t, j);
+            if (!ok) break;
+            if (j == nt(t) - 1) ptx::mma_commit(&ctl->o_full[t]);
+            if (t == last_pv) ptx::mma_commit(&ctl->v_empty[j % NSTAGE]);
+          }
+          if (j + 1 < nt(t)) {
+            ok = issue_qk(t, j + 1);
+            if (!ok) break;
+            if (t == last_qk) ptx::mma_commit(&ctl->k_empty[(j + 1) % NSTAGE]);
+          }
+        }
       }
     }
+  }
   } else {
+    ptx::setmaxnreg_inc<216>();
     // ------------------------------------------------------------- softmax --
-    const int row = row0 + tid;                                   // global query row of this thread
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;  // TMEM lane quarter of this warp
+    const int t = warp >> 2;                     // query tile of this warpgroup
+    const int r_in = tid & (BM - 1);             // row within the tile = TMEM lane
+    const int row = row0 + t * BM + r_in;        // global query row
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + t * 128 + lane_addr;
+    const uint32_t tO = tmem + 256 + t * D + lane_addr;
     const float c = fabsf(a.scale) * kLog2e;
+    const float2 c2 = make_float2(c, c);
+    const int n_t = nt(t);
     float m_ref = -INFINITY;  // reference max, in scaled log2 units
-    float l = 0.f;
+    float2 l2 = make_float2(0.f, 0.f);
     bool ok = true;
-    uint32_t r[32];
+    uint32_t s[BN];
 
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const uint32_t ph = static_cast<uint32_t>(j & 1);
-      ok = ptx::mbar_wait(&ctl->s_full, ph, abort_flag);
+    for (int j = 0; j < n_t && ok; ++j) {
+      ok = ptx::mbar_wait(&ctl->s_full[t], static_cast<uint32_t>(j & 1), abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
-      const int col0 = j * BN;
-      // Highest valid column of this row within the tile.
-      int lim = kv_len - 1 - col0;
-      if (a.causal && row - col0 < lim) lim = row - col0;
-      const bool mask_tile = (col0 + BN > kv_len) || (a.causal && col0 + BN - 1 > row0);
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) ptx::tmem_ld32p(tS + cc * 32, s + cc * 32);
+      ptx::tmem_wait_ld();
 
-      // pass 1: row max
-      float mx = -INFINITY;
+      const int col0 = j * BN;
+      const bool mask_tile = (col0 + BN > kv_len) || (a.causal && col0 + BN - 1 > row0 + t * BM);
+      if (mask_tile) {
+        // Highest valid column of this row within the tile.
+        int lim = kv_len - 1 - col0;
+        if (a.causal && row - col0 < lim) lim = row - col0;
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        ptx::tmem_ld32(tS + lane_addr + cc * 32, r);
-        ptx::tmem_wait_ld();
-        if (mask_tile) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (cc * 32 + i > lim) r[i] = 0xff800000u;  // -inf
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+        for (int i = 0; i < BN; ++i)
+          if (i > lim) s[i] = 0xff800000u;  // -inf
       }
-      const float x_max = mx * c;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
+        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])));
+      }
+      const float x_max = fmaxf(mx0, mx1) * c;
       if (j == 0) {
         m_ref = x_max;
       } else {
@@ -232,52 +288,52 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (__any_sync(0xffffffffu, grow)) {
           const float m_new = grow ? x_max : m_ref;
           const float alpha = grow ? ptx::ex2(m_ref - m_new) : 1.f;
+          uint32_t r[32];
 #pragma unroll
           for (int cc = 0; cc < D / 32; ++cc) {
-            ptx::tmem_ld32(tO + lane_addr + cc * 32, r);
+            ptx::tmem_ld32(tO + cc * 32, r);
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            ptx::tmem_st32(tO + lane_addr + cc * 32, r);
+            ptx::tmem_st32(tO + cc * 32, r);
           }
-          l *= alpha;
+          l2.x *= alpha, l2.y *= alpha;
           m_ref = m_new;
         }
       }
-      // pass 2: P = 2^(c*s - m_ref), row sum, packed 16-bit P over the S columns
+      // P = 2^(c*s - m_ref) in packed fp32 pairs; two halves of 64 columns so that
+      // the packed 16-bit P of the first half is stored while the second is computed.
+      const float2 nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        ptx::tmem_ld32(tS + lane_addr + cc * 32, r);
-        ptx::tmem_wait_ld();
-        uint32_t pk[16];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ptx::ex2(fmaf(__uint_as_float(r[i]), c, -m_ref));
-          float p1 = ptx::ex2(fmaf(__uint_as_float(r[i + 1]), c, -m_ref));
-          if (mask_tile) {
-            if (cc * 32 + i > lim) p0 = 0.f;
-            if (cc * 32 + i + 1 > lim) p1 = 0.f;
-          }
-          l += p0 + p1;
-          pk[i >> 1] = pack2<BF16>(p0, p1);
+        for (int i = 0; i < 64; i += 2) {
+          const int e = hf * 64 + i;
+          float2 x = ptx::fma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nm2);
+          float2 p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
+          l2 = ptx::add2(l2, p);
+          pk[i >> 1] = pack2<BF16>(p.x, p.y);
         }
-        ptx::tmem_st16(tS + lane_addr + cc * 16, pk);
+        ptx::tmem_st32(tS + hf * 32, pk);
       }
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(&ctl->p_full);
+      ptx::mbar_arrive(&ctl->p_full[t]);
     }
 
     // epilogue: O / l -> global, LSE
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     T* orow = reinterpret_cast<T*>(a.o) + b * a.os.b + h * a.os.h + static_cast<int64_t>(row) * a.os.s;
-    if (n_tiles > 0) {
-      if (ok) ok = ptx::mbar_wait(&ctl->o_full, 0, abort_flag);
+    const float l = l2.x + l2.y;
+    if (n_t > 0) {
+      if (ok) ok = ptx::mbar_wait(&ctl->o_full[t], 0, abort_flag);
       ptx::tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      uint32_t r[32];
 #pragma unroll
       for (int cc = 0; cc < D / 32; ++cc) {
-        ptx::tmem_ld32(tO + lane_addr + cc * 32, r);
+        ptx::tmem_ld32(tO + cc * 32, r);
         ptx::tmem_wait_ld();
         if (ok && row < a.Lq) {
 #pragma unroll
@@ -303,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
@@ -353,7 +409,7 @@ cudaError_t launch_t(const FwdArgs& a, int dtype, cudaStream_t stream) {
   auto kern = fwd_tc_kernel<D, BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
   if (e != cudaSuccess) return e;
-  dim3 grid((a.Lq + BM - 1) / BM, a.Hq, a.B);
+  dim3 grid((a.Lq + QT * BM - 1) / (QT * BM), a.Hq, a.B);
   kern<<<grid, kThreads, smem_bytes<D>(), stream>>>(tq, tk, tv, a);
   return cudaGetLastError();
 }
