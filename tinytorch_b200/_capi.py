@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libtt_attn.so")
+# TT_ATTN_LIB selects another build of the same library (e.g. a tuning variant).
+LIB_PATH = os.environ.get("TT_ATTN_LIB") or os.path.join(HERE, "lib", "libtt_attn.so")
 
 F32, F16, BF16 = 0, 1, 2
 KIND_FWD, KIND_BWD, KIND_DECODE = 0, 1, 2

@@ -30,12 +30,12 @@ def _headers_mtime():
     return max(os.path.getmtime(h) for h in hs)
 
 
-def _compile(src, verbose):
-    obj = os.path.join(OUT, src[:-3] + ".o")
+def _compile(src, verbose, out_dir=None, defines=()):
+    obj = os.path.join(out_dir or OUT, src[:-3] + ".o")
     spath = os.path.join(CSRC, src)
     if os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(spath), _headers_mtime()):
         return obj
-    cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", spath, "-o", obj]
+    cmd = [NVCC] + FLAGS + ["-D" + d for d in defines] + (["-Xptxas", "-v"] if verbose else []) + ["-c", spath, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
@@ -44,16 +44,21 @@ def _compile(src, verbose):
     return obj
 
 
-def build(verbose=False, force=False):
-    os.makedirs(OUT, exist_ok=True)
+def build(verbose=False, force=False, out_dir=None, defines=()):
+    """Build into `out_dir` (default lib/).  `defines` are extra -D macros, used to
+    build tuning variants side by side; load one with TT_ATTN_LIB=<path>."""
+    out = out_dir or OUT
+    lib = os.path.join(out, "libtt_attn.so")
+    os.makedirs(out, exist_ok=True)
     if force:
-        for f in os.listdir(OUT):
+        for f in os.listdir(out):
             if f.endswith((".o", ".so")):
-                os.remove(os.path.join(OUT, f))
+                os.remove(os.path.join(out, f))
     with cf.ThreadPoolExecutor(max_workers=8) as ex:
-        objs = list(ex.map(lambda s: _compile(s, verbose), _sources()))
-    if os.path.exists(LIB) and os.path.getmtime(LIB) > max(os.path.getmtime(o) for o in objs):
-        return LIB
+        objs = list(ex.map(lambda s: _compile(s, verbose, out, defines), _sources()))
+    if os.path.exists(lib) and os.path.getmtime(lib) > max(os.path.getmtime(o) for o in objs):
+        return lib
+    LIB = lib
     # cudart is linked statically (nvcc default), so the library loads on a
     # machine without a driver; the driver's tensor-map encoder is looked up at
     # run time through cudaGetDriverEntryPoint.
@@ -65,4 +70,6 @@ def build(verbose=False, force=False):
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
+    outs = [a[6:] for a in sys.argv[1:] if a.startswith("--out=")]
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, out_dir=outs[0] if outs else None, defines=defs))

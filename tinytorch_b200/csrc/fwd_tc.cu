@@ -40,6 +40,27 @@ constexpr int NSTAGE = 2;    // K/V ring depth
 constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the producer and issuer warps
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef TT_POLY_NUM
+#define TT_POLY_NUM 0
+#endif
+#ifndef TT_POLY_DEN
+#define TT_POLY_DEN 4
+#endif
+constexpr int kPolyNum = TT_POLY_NUM, kPolyDen = TT_POLY_DEN;
+
+// Developer aid, compiled out by default: with -DTT_ATTN_PROFILE the first CTA
+// writes clock64() stamps of its pipeline phases to the buffer passed as `status`
+// (int64 [3][64][8]: softmax warpgroup 0, softmax warpgroup 1, issuer).
+#ifdef TT_ATTN_PROFILE
+#define TT_STAMP(who, j, slot)                                                                          \
+  do {                                                                                                  \
+    if (prof && (j) < 64) prof[((who)*64 + (j)) * 8 + (slot)] = clock64();                              \
+  } while (0)
+#else
+#define TT_STAMP(who, j, slot) \
+  do {                         \
+  } while (0)
+#endif
 
 struct __align__(8) SmemCtl {
   uint64_t q_full;
@@ -74,6 +95,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
+#ifdef TT_ATTN_PROFILE
+  const long long t_entry = clock64();
+#endif
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int TB = tile_bytes<D>();
@@ -108,6 +132,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int n_max = nt0 > nt1 ? nt0 : nt1;
   auto nt = [&](int t) { return t == 0 ? nt0 : nt1; };
 
+  constexpr int HALVES = D / 64;  // 64-element (128-byte) column blocks per row
+  constexpr int HALF_BYTES = BM * 128;
+
   if (warp == 8 && lane == 0) {
     ptx::mbar_init(&ctl->q_full, 1);
 #pragma unroll
@@ -125,9 +152,25 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
-    ptx::tma_prefetch_desc(&tmQ);
-    ptx::tma_prefetch_desc(&tmK);
-    ptx::tma_prefetch_desc(&tmV);
+    // The first loads do not depend on anything the other warps set up: start
+    // them before the CTA-wide barrier so that their latency overlaps the TMEM
+    // allocation.
+    if (n_max > 0) {
+      ptx::mbar_arrive_expect_tx(&ctl->q_full, QT * TB);
+#pragma unroll
+      for (int t = 0; t < QT; ++t)
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf)
+          ptx::tma_load_4d(sQ + t * TB + hf * HALF_BYTES, &tmQ, &ctl->q_full, hf * 64, row0 + t * BM, h, b);
+      ptx::mbar_arrive_expect_tx(&ctl->k_full[0], TB);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf)
+        ptx::tma_load_4d(sK + hf * HALF_BYTES, &tmK, &ctl->k_full[0], hf * 64, 0, hk, b);
+      ptx::mbar_arrive_expect_tx(&ctl->v_full[0], TB);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf)
+        ptx::tma_load_4d(sV + hf * HALF_BYTES, &tmV, &ctl->v_full[0], hf * 64, 0, hk, b);
+    }
   }
   if (warp == 9) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -137,10 +180,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
+#ifdef TT_ATTN_PROFILE
+  long long* prof = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 &&
+                     (warp == 0 || warp == 4 || warp == 9) && a.status)
+                        ? reinterpret_cast<long long*>(a.status)
+                        : nullptr;
+  // per-CTA summary for the CTAs of (head 0, batch 0): [blockIdx.x][8] after the per-iteration area
+  long long* psum = (blockIdx.y == 0 && blockIdx.z == 0 && tid == 0 && a.status && blockIdx.x < 32)
+                        ? reinterpret_cast<long long*>(a.status) + 3 * 64 * 8 + blockIdx.x * 8
+                        : nullptr;
+  if (psum) psum[0] = t_entry, psum[1] = clock64(), psum[7] = nt1;
+#endif
   // TMEM columns: S_t (fp32, 128) at t*128, P_t (16-bit pairs) overlays S_t[0,64); O_t (fp32, D) at 256 + t*D.
-
-  constexpr int HALVES = D / 64;  // 64-element (128-byte) column blocks per row
-  constexpr int HALF_BYTES = BM * 128;
 
   // Register budget: the softmax warpgroups hold a whole 128-column S row per
   // thread; the producer / issuer warpgroup needs almost nothing.
@@ -149,13 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 8) {
     // ------------------------------------------------------------ producer --
     if (lane == 0 && n_max > 0) {
-      ptx::mbar_arrive_expect_tx(&ctl->q_full, QT * TB);
-#pragma unroll
-      for (int t = 0; t < QT; ++t)
-#pragma unroll
-        for (int hf = 0; hf < HALVES; ++hf)
-          ptx::tma_load_4d(sQ + t * TB + hf * HALF_BYTES, &tmQ, &ctl->q_full, hf * 64, row0 + t * BM, h, b);
-      for (int j = 0; j < n_max; ++j) {
+      for (int j = 1; j < n_max; ++j) {  // tile 0 was requested during set-up
         const int st = j % NSTAGE;
         const uint32_t ph = static_cast<uint32_t>((j / NSTAGE) & 1);
         if (!ptx::mbar_wait(&ctl->k_empty[st], ph ^ 1, abort_flag)) break;
@@ -182,36 +227,45 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t neg = a.scale < 0.f ? (1u << 13) : 0u;
       const uint32_t idesc_qk = ptx::make_idesc_f16(BM, BN, BF16 ? 1 : 0, 0, 0) | neg;
       const uint32_t idesc_pv = ptx::make_idesc_f16(BM, D, BF16 ? 1 : 0, 0, 1);
-      const uint32_t aQ = ptx::smem_u32(sQ), aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV);
+      // Descriptor words are prepared once; inside the loops stepping to the next
+      // k-slice or ring stage is a single 32-bit add, so that the issuing thread
+      // keeps pace with the tensor pipe (one 128x128x16 MMA per 64 cycles).
+      constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
+      const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16);
+      const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
+      const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), HALF_BYTES);
       bool ok = ptx::mbar_wait(&ctl->q_full, 0, abort_flag);
 
       auto issue_qk = [&](int t, int j) -> bool {
         const int st = j % NSTAGE;
         if (!ptx::mbar_wait(&ctl->k_full[st], static_cast<uint32_t>((j / NSTAGE) & 1), abort_flag)) return false;
+        TT_STAMP(2, j, t * 4 + 3);
         ptx::tc_fence_after();
+        const uint32_t a0 = qlo + t * (TB >> 4), b0 = klo + st * (TB >> 4), d = tmem + t * 128;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          // K-major operands: 64-element halves 16 KB apart, 32 bytes per k-step
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          ptx::mma_ss(tmem + t * 128, ptx::make_smem_desc_sw128(aQ + t * TB + off, 16, 1024),
-                      ptx::make_smem_desc_sw128(aK + st * TB + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+          // K-major operands: 64-element halves HALF_BYTES apart, 32 bytes per k-step
+          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          ptx::mma_ss2(d, a0 + off, kHi, b0 + off, kHi, idesc_qk, ks > 0 ? 1u : 0u);
         }
         ptx::mma_commit(&ctl->s_full[t]);
+        TT_STAMP(2, j, t * 4 + 2);
         return true;
       };
       auto issue_pv = [&](int t, int j) -> bool {
         const int st = j % NSTAGE;
         if (!ptx::mbar_wait(&ctl->v_full[st], static_cast<uint32_t>((j / NSTAGE) & 1), abort_flag)) return false;
         if (!ptx::mbar_wait(&ctl->p_full[t], static_cast<uint32_t>(j & 1), abort_flag)) return false;
+        TT_STAMP(2, j, t * 4 + 0);
         ptx::tc_fence_after();
+        const uint32_t b0 = vlo + st * (TB >> 4), d = tmem + 256 + t * D, a0 = tmem + t * 128;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           // V is N(=D)-contiguous: 16 keys per k-step = 2048 bytes; the two
           // 64-wide column blocks of D=128 are HALF_BYTES apart (LBO).
-          ptx::mma_ts(tmem + 256 + t * D, tmem + t * 128 + ks * 8,
-                      ptx::make_smem_desc_sw128(aV + st * TB + ks * 2048, HALF_BYTES, 1024), idesc_pv,
-                      (j > 0 || ks > 0) ? 1u : 0u);
+          ptx::mma_ts2(d, a0 + ks * 8, b0 + ks * (2048 >> 4), kHi, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
+        TT_STAMP(2, j, t * 4 + 1);
         return true;
       };
 
@@ -257,12 +311,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t s[BN];
 
     for (int j = 0; j < n_t && ok; ++j) {
+      TT_STAMP(t, j, 0);
       ok = ptx::mbar_wait(&ctl->s_full[t], static_cast<uint32_t>(j & 1), abort_flag);
       if (!ok) break;
+      TT_STAMP(t, j, 1);
       ptx::tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) ptx::tmem_ld32p(tS + cc * 32, s + cc * 32);
       ptx::tmem_wait_ld();
+      TT_STAMP(t, j, 2);
 
       const int col0 = j * BN;
       const bool mask_tile = (col0 + BN > kv_len) || (a.causal && col0 + BN - 1 > row0 + t * BM);
@@ -274,13 +331,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < BN; ++i)
           if (i > lim) s[i] = 0xff800000u;  // -inf
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY;
+      // eight independent 3-input max chains over the 128 columns
+      float mx[8];
 #pragma unroll
-      for (int i = 0; i < BN; i += 4) {
-        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
-        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])));
-      }
-      const float x_max = fmaxf(mx0, mx1) * c;
+      for (int q = 0; q < 8; ++q) mx[q] = ptx::max3(__uint_as_float(s[q]), __uint_as_float(s[q + 8]), -INFINITY);
+#pragma unroll
+      for (int i = 16; i < BN; i += 16)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) mx[q] = ptx::max3(mx[q], __uint_as_float(s[i + q]), __uint_as_float(s[i + q + 8]));
+      const float x_max =
+          ptx::max3(ptx::max3(mx[0], mx[1], mx[2]), ptx::max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
       if (j == 0) {
         m_ref = x_max;
       } else {
@@ -303,6 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       // P = 2^(c*s - m_ref) in packed fp32 pairs; two halves of 64 columns so that
       // the packed 16-bit P of the first half is stored while the second is computed.
+      TT_STAMP(t, j, 3);
       const float2 nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
@@ -311,15 +372,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < 64; i += 2) {
           const int e = hf * 64 + i;
           float2 x = ptx::fma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nm2);
-          float2 p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
+          // kPolyNum of every kPolyDen pairs take their exponential on the FMA
+          // pipe, the rest on the special-function unit, so that both pipes work.
+          float2 p;
+          if ((i >> 1) % kPolyDen < kPolyNum) {
+            p = ptx::ex2_poly2(x);
+          } else {
+            p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
+          }
           l2 = ptx::add2(l2, p);
           pk[i >> 1] = pack2<BF16>(p.x, p.y);
         }
         ptx::tmem_st32(tS + hf * 32, pk);
       }
+      TT_STAMP(t, j, 4);
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&ctl->p_full[t]);
+      TT_STAMP(t, j, 5);
     }
 
     // epilogue: O / l -> global, LSE
@@ -327,7 +397,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     T* orow = reinterpret_cast<T*>(a.o) + b * a.os.b + h * a.os.h + static_cast<int64_t>(row) * a.os.s;
     const float l = l2.x + l2.y;
     if (n_t > 0) {
+#ifdef TT_ATTN_PROFILE
+      if (psum) psum[2] = clock64();
+#endif
       if (ok) ok = ptx::mbar_wait(&ctl->o_full[t], 0, abort_flag);
+#ifdef TT_ATTN_PROFILE
+      if (psum) psum[3] = clock64();
+#endif
       ptx::tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       uint32_t r[32];
@@ -357,12 +433,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
+#ifdef TT_ATTN_PROFILE
+  if (psum) psum[4] = clock64();
+#endif
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 9) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
+#ifdef TT_ATTN_PROFILE
+  if (psum) psum[5] = clock64();
+#endif
   if (tid == 0 && ctl->abort_flag && a.status) atomicOr(a.status, kStatusWaitExpired);
 }
 

@@ -182,6 +182,15 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr, uint32_
   return d;
 }
 
+// The same descriptor split in two words: `hi` is constant for a layout, `lo`
+// holds the (16-byte) start address, so stepping through a tile is one 32-bit add.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr >> 4) & 0x3fff) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | (2u << 29);
+}
+
 // 32-bit instruction descriptor for kind::f16 with fp32 accumulation.
 //   ab_fmt: 0 = f16, 1 = bf16;  b_mn_major: B operand is N-contiguous in smem.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, int ab_fmt, int a_mn_major, int b_mn_major) {
@@ -216,6 +225,36 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Variants taking the descriptors as (lo, hi) words.
+__device__ __forceinline__ void mma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on `bar` once every tcgen05 operation issued so far by this thread
 // has completed (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
@@ -248,6 +287,47 @@ __device__ __forceinline__ void setmaxnreg_inc() {
 template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+// a + b rounded toward minus infinity (used to take floor() through a magic constant).
+__device__ __forceinline__ float2 add2_rm(float2 a, float2 b) {
+  uint64_t d;
+  asm("add.rm.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x for a pair of finite or -inf inputs, on the FMA pipe instead of the special-
+// function unit: x = n + f with n = floor(x), 2^f by a cubic fitted on [0, 1]
+// (p(0) = 1 exactly, relative error < 9e-5), 2^n by placing n + 127 in the exponent
+// field.  floor() comes from adding 1.5 * 2^23 + 127 with round-down: the sum's low
+// mantissa bits then hold n + 127.  Inputs below -126 are clamped (result 2^-126).
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  const float kMagic = 12582912.f + 127.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 y = add2_rm(x, make_float2(kMagic, kMagic));
+  const float2 n = add2(y, make_float2(-kMagic, -kMagic));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = fma2(f, make_float2(0.07706470787525177f, 0.07706470787525177f),
+                  make_float2(0.2276475429534912f, 0.2276475429534912f));
+  p = fma2(p, f, make_float2(0.6951162219047546f, 0.6951162219047546f));
+  p = fma2(p, f, make_float2(1.f, 1.f));
+  const float2 sc = make_float2(__uint_as_float(__float_as_uint(y.x) << 23), __uint_as_float(__float_as_uint(y.y) << 23));
+  return mul2(p, sc);
 }
 
 __device__ __forceinline__ float ex2(float x) {
