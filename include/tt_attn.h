@@ -199,7 +199,8 @@ TT_ATTN_API int tt_attn_decode(const tt_attn_decode_params* p);
 #define TT_ATTN_STATIC_SCRATCH_BYTES (24u << 20)
 TT_ATTN_API int tt_attn_decode_static(const tt_attn_decode_params* p);
 
-/* Scratch bytes the given call needs (0 if none).  Skv is the cache capacity
+/* Scratch bytes the given call needs (0 if none; the fp16/bf16 forward needs a
+ * 256-byte block for its work counter).  Skv is the cache capacity
  * for TT_ATTN_KIND_DECODE. */
 TT_ATTN_API size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int Lq, int Skv, int D);
 

@@ -101,9 +101,10 @@ const char* tt_attn_strerror(int status) {
 }
 
 size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int Lq, int Skv, int D) {
-  (void)dtype;
   (void)Hkv;
   if (B <= 0 || Hq <= 0 || D <= 0) return 0;
+  // fp16 / bf16 forward: one work counter for the persistent kernel's scheduler
+  if (kind == TT_ATTN_KIND_FWD) return dtype == TT_ATTN_F32 ? 0 : 256;
   if (kind == TT_ATTN_KIND_BWD) return round256(static_cast<size_t>(B) * Hq * (Lq > 0 ? Lq : 0) * sizeof(float));
   if (kind == TT_ATTN_KIND_DECODE) {
     if (Skv <= 0) return 0;
@@ -137,6 +138,10 @@ int tt_attn_fwd(const tt_attn_fwd_params* p) {
   a.status = p->status;
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  Workspace ws;
+  const size_t need = tt_attn_workspace_bytes(TT_ATTN_KIND_FWD, p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D);
+  if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
+  a.sched = static_cast<int*>(ws.ptr);
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   cudaError_t e = p->dtype == TT_ATTN_F32 ? launch_fwd_simt(p->dtype, p->D, a, stream)
                                           : launch_fwd_tc(p->dtype, p->D, a, p->device, stream);

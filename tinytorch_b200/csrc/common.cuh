@@ -37,6 +37,7 @@ struct FwdArgs {
   float scale;
   const int32_t* kv_lens;
   int32_t* status;
+  int* sched;  // tensor-core path: work counter in scratch memory, zeroed by the launcher
 };
 
 struct BwdArgs {
