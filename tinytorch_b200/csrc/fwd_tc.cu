@@ -86,9 +86,10 @@ template <int D>
 constexpr int tile_bytes() {
   return BM * D * 2;
 }
+constexpr int kStageBytes = BM * 128;  // per warpgroup: one 64-column block of an O tile
 template <int D>
 constexpr int smem_bytes() {
-  return (QT + 2 * NSTAGE) * tile_bytes<D>() + 1024 /*alignment slack*/ + 256 /*SmemCtl*/;
+  return (QT + 2 * NSTAGE) * tile_bytes<D>() + QT * kStageBytes + 1024 /*alignment slack*/ + 256 /*SmemCtl*/;
 }
 
 template <bool BF16>
@@ -136,7 +137,8 @@ __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
     fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const FwdArgs a) {
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                  const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -144,7 +146,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* sQ = smem;                    // QT tiles
   uint8_t* sK = smem + QT * TB;          // NSTAGE tiles
   uint8_t* sV = sK + NSTAGE * TB;        // NSTAGE tiles
-  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(sV + NSTAGE * TB);
+  uint8_t* sO = sV + NSTAGE * TB;        // QT staging blocks for the O stores
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(sO + QT * kStageBytes);
   volatile int* abort_flag = &ctl->abort_flag;
 
   const int tid = threadIdx.x;
@@ -182,6 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tma_prefetch_desc(&tmQ);
     ptx::tma_prefetch_desc(&tmK);
     ptx::tma_prefetch_desc(&tmV);
+    ptx::tma_prefetch_desc(&tmO);
   }
   if (warp == 9) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -360,10 +364,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     long long* prof = (blockIdx.x == 0 && r_in == 0 && a.status) ? reinterpret_cast<long long*>(a.status) : nullptr;
 #endif
 
-    for (uint32_t i = 0; ok; ++i) {
+    // The warpgroup meets at named barriers in the epilogue, so its threads must
+    // leave the loop together: an expired wait is voted on (twice per item) and
+    // then every thread of the warpgroup unwinds.
+    for (uint32_t i = 0;; ++i) {
       const int slot = i & 1;
       TT_STAMP(0);
-      if (!ptx::mbar_wait(&ctl->item_full[slot], (i >> 1) & 1, abort_flag)) break;
+      ok = ptx::mbar_wait(&ctl->item_full[slot], (i >> 1) & 1, abort_flag);
+      if (ptx::named_barrier_or(1 + t, BM, !ok)) break;
       const int w = ctl->item[slot];
       ptx::mbar_arrive(&ctl->item_empty[slot]);
       if (w < 0) break;
@@ -475,6 +483,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // next item's first S_t; its first PV waits for this warpgroup's next P.
       if (ok) ok = ptx::mbar_wait(&ctl->o_full[t], ec & 1, abort_flag);
       ++ec;
+      if (ptx::named_barrier_or(1 + t, BM, !ok)) break;
       TT_STAMP(4);
       ptx::tc_fence_after();
 #pragma unroll
@@ -483,20 +492,35 @@ __global__ void __launch_bounds__(kThreads, 1)
       TT_STAMP(5);
       const float l = l2.x + l2.y;
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      if (ok && row < a.Lq) {
+      // O leaves through shared memory and TMA stores (coalesced; rows beyond Lq
+      // are clipped by the tensor map): one 64-column block at a time, written in
+      // the 128-byte-swizzled layout the map expects.
+      uint8_t* stage = sO + t * kStageBytes;
 #pragma unroll
-        for (int e = 0; e < D; e += 8) {
+      for (int hf = 0; hf < HALVES; ++hf) {
+        if (r_in == 0) ptx::bulk_wait_read();  // previous store out of this block has been read
+        ptx::named_barrier(1 + t, BM);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const int e = hf * 64 + ch * 8;
           uint4 wv;
           wv.x = pack2<BF16>(__uint_as_float(s[e + 0]) * inv, __uint_as_float(s[e + 1]) * inv);
           wv.y = pack2<BF16>(__uint_as_float(s[e + 2]) * inv, __uint_as_float(s[e + 3]) * inv);
           wv.z = pack2<BF16>(__uint_as_float(s[e + 4]) * inv, __uint_as_float(s[e + 5]) * inv);
           wv.w = pack2<BF16>(__uint_as_float(s[e + 6]) * inv, __uint_as_float(s[e + 7]) * inv);
-          *reinterpret_cast<uint4*>(orow + e) = wv;
+          *reinterpret_cast<uint4*>(stage + r_in * 128 + ((ch ^ (r_in & 7)) << 4)) = wv;
         }
-        if (lse_row) *lse_row = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+        ptx::fence_proxy_async_smem();
+        ptx::named_barrier(1 + t, BM);
+        if (r_in == 0 && ok) {
+          ptx::tma_store_4d(&tmO, stage, hf * 64, tile_row0, it.h, it.b);
+          ptx::bulk_commit();
+        }
       }
+      if (ok && row < a.Lq && lse_row) *lse_row = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
       TT_STAMP(6);
     }
+    if (r_in == 0) ptx::bulk_wait_all();
   }
 
   ptx::tc_fence_before();
@@ -555,9 +579,9 @@ int sm_count(int device) {
 
 template <int D, bool BF16>
 cudaError_t launch_t(const FwdArgs& a, int dtype, int device, cudaStream_t stream) {
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   if (!make_map(&tq, dtype, a.q, D, a.Lq, a.Hq, a.B, a.qs) || !make_map(&tk, dtype, a.k, D, a.Skv, a.Hkv, a.B, a.ks) ||
-      !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs))
+      !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs) || !make_map(&to, dtype, a.o, D, a.Lq, a.Hq, a.B, a.os))
     return cudaErrorInvalidValue;
   auto kern = fwd_tc_kernel<D, BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
@@ -568,7 +592,7 @@ cudaError_t launch_t(const FwdArgs& a, int dtype, int device, cudaStream_t strea
   const long long n_items = static_cast<long long>((a.Lq + QT * BM - 1) / (QT * BM)) * a.Hq * a.B;
   const int sms = sm_count(device);
   const int grid = static_cast<int>(n_items < sms ? n_items : sms);
-  kern<<<grid, kThreads, smem_bytes<D>(), stream>>>(tq, tk, tv, a);
+  kern<<<grid, kThreads, smem_bytes<D>(), stream>>>(tq, tk, tv, to, a);
   return cudaGetLastError();
 }
 
