@@ -418,59 +418,77 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int e = 0; e < BN; ++e)
             if (e > lim) s[e] = 0xff800000u;  // -inf
         }
-        // eight independent 3-input max chains over the 128 columns
-        float mx[8];
+        // The row maximum is only a reference point for the exponentials, so it is
+        // not recomputed for every tile: after the first tile the row keeps its
+        // reference as long as the tile's exponentials stay small, which the tile's
+        // own row sum shows (all terms are positive: sum <= 2^8 implies every term
+        // <= 2^8).  Only when the sum is larger (or not finite) is the maximum of
+        // the tile taken, O and the running sum rescaled, and the tile redone.
+        bool need_max = (j == 0);
+        for (;;) {
+          if (need_max) {
+            // eight independent 3-input max chains over the 128 columns
+            float mx[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) mx[q] = ptx::max3(__uint_as_float(s[q]), __uint_as_float(s[q + 8]), -INFINITY);
+            for (int q = 0; q < 8; ++q)
+              mx[q] = ptx::max3(__uint_as_float(s[q]), __uint_as_float(s[q + 8]), -INFINITY);
 #pragma unroll
-        for (int e = 16; e < BN; e += 16)
+            for (int e = 16; e < BN; e += 16)
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            mx[q] = ptx::max3(mx[q], __uint_as_float(s[e + q]), __uint_as_float(s[e + q + 8]));
-        const float x_max =
-            ptx::max3(ptx::max3(mx[0], mx[1], mx[2]), ptx::max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
-        if (j == 0) {
-          m_ref = x_max;
-        } else {
-          const bool grow = x_max - m_ref > kRescaleThreshold;
-          if (__any_sync(0xffffffffu, grow)) {
-            const float m_new = grow ? x_max : m_ref;
-            const float alpha = grow ? ptx::ex2(m_ref - m_new) : 1.f;
-            uint32_t r[32];
+              for (int q = 0; q < 8; ++q)
+                mx[q] = ptx::max3(mx[q], __uint_as_float(s[e + q]), __uint_as_float(s[e + q + 8]));
+            const float x_max =
+                ptx::max3(ptx::max3(mx[0], mx[1], mx[2]), ptx::max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
+            if (j == 0) {
+              m_ref = x_max;
+            } else if (x_max > m_ref) {
+              const float alpha = ptx::ex2(m_ref - x_max);
+              uint32_t r[32];
 #pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {
-              ptx::tmem_ld32(tO + cc * 32, r);
-              ptx::tmem_wait_ld();
+              for (int cc = 0; cc < D / 32; ++cc) {
+                ptx::tmem_ld32(tO + cc * 32, r);
+                ptx::tmem_wait_ld();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-              ptx::tmem_st32(tO + cc * 32, r);
+                for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                ptx::tmem_st32(tO + cc * 32, r);
+              }
+              l2.x *= alpha, l2.y *= alpha;
+              m_ref = x_max;
             }
-            l2.x *= alpha, l2.y *= alpha;
-            m_ref = m_new;
           }
-        }
-        // P = 2^(c*s - m_ref) in packed fp32 pairs; two halves of 64 columns so that
-        // the packed 16-bit P of the first half is stored while the second is computed.
-        const float2 nm2 = make_float2(-m_ref, -m_ref);
+          // P = 2^(c*s - m_ref) in packed fp32 pairs; two halves of 64 columns so that
+          // the packed 16-bit P of the first half is stored while the second is computed.
+          const float2 nm2 = make_float2(-m_ref, -m_ref);
+          float2 lt = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t pk[32];
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t pk[32];
 #pragma unroll
-          for (int e2 = 0; e2 < 64; e2 += 2) {
-            const int e = hf * 64 + e2;
-            float2 x = ptx::fma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nm2);
-            // kPolyNum of every kPolyDen pairs take their exponential on the FMA
-            // pipe, the rest on the special-function unit, so that both pipes work.
-            float2 p;
-            if ((e2 >> 1) % kPolyDen < kPolyNum) {
-              p = ptx::ex2_poly2(x);
-            } else {
-              p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
+            for (int e2 = 0; e2 < 64; e2 += 2) {
+              const int e = hf * 64 + e2;
+              float2 x = ptx::fma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nm2);
+              // kPolyNum of every kPolyDen pairs take their exponential on the FMA
+              // pipe, the rest on the special-function unit.
+              float2 p;
+              if ((e2 >> 1) % kPolyDen < kPolyNum) {
+                p = ptx::ex2_poly2(x);
+              } else {
+                p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
+              }
+              lt = ptx::add2(lt, p);
+              pk[e2 >> 1] = pack2<BF16>(p.x, p.y);
             }
-            l2 = ptx::add2(l2, p);
-            pk[e2 >> 1] = pack2<BF16>(p.x, p.y);
+            ptx::tmem_st32(tS + hf * 32, pk);
           }
-          ptx::tmem_st32(tS + hf * 32, pk);
+          const float tile_sum = lt.x + lt.y;
+          // redo with a fresh maximum if any row of the warp needs it (tcgen05.ld /
+          // .st are warp-collective, so the warp decides together)
+          const bool redo = !need_max && !(tile_sum <= 256.f);
+          if (!__any_sync(0xffffffffu, redo)) {
+            l2 = ptx::add2(l2, lt);
+            break;
+          }
+          need_max = true;
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
