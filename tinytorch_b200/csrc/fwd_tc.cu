@@ -49,14 +49,6 @@ constexpr int NSTAGE = 2;    // K/V ring depth
 constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the producer and issuer warps
 constexpr int kTmemCols = 512;
 constexpr int kItemConsumers = 1 + QT * BM;  // issuer thread + every softmax thread
-constexpr float kRescaleThreshold = 8.0f;    // log2 units
-#ifndef TT_POLY_NUM
-#define TT_POLY_NUM 0
-#endif
-#ifndef TT_POLY_DEN
-#define TT_POLY_DEN 4
-#endif
-constexpr int kPolyNum = TT_POLY_NUM, kPolyDen = TT_POLY_DEN;
 
 // Developer aid, compiled out by default: with -DTT_ATTN_PROFILE the first CTA
 // writes clock64() stamps per work item to the buffer passed as `status`
@@ -66,9 +58,16 @@ constexpr int kPolyNum = TT_POLY_NUM, kPolyDen = TT_POLY_DEN;
   do {                                                                              \
     if (prof && i < 32) prof[(t * 32 + i) * 8 + (slot)] = clock64();               \
   } while (0)
+#define TT_FINE(slot)                                                                              \
+  do {                                                                                              \
+    if (prof && i == 3 && j < 64) prof[2 * 32 * 8 + (t * 64 + j) * 4 + (slot)] = clock64();        \
+  } while (0)
 #else
 #define TT_STAMP(slot) \
   do {                 \
+  } while (0)
+#define TT_FINE(slot) \
+  do {                \
   } while (0)
 #endif
 
@@ -108,12 +107,37 @@ struct Item {
   int b, h, hk, row0, kv_len, nt0, nt1, n_max;
 };
 
+// Item order.  Under the causal mask a pair of query tiles costs in proportion
+// to its position, so pairs are dealt in kPasses passes over the heads: the latest
+// (longest) quarter of every head first, the earliest (shortest) quarter last, and
+// within a pass head by head, longest pair first.  CTAs running at the same time
+// then share few heads' K/V in L2, and the items drawn last, which decide how long
+// the other SMs idle at the end, are the shortest ones.
+constexpr int kPasses = 4;
+
 __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs) {
   Item it;
-  const int bh = w / n_pairs;
-  const int mp = n_pairs - 1 - (w - bh * n_pairs);  // longest pair of the head first
+  const int n_bh = a.Hq * a.B;
+  int bh, mp;
+  if (n_pairs >= 2 * kPasses) {
+    // pass p covers pairs [lo_p, hi_p) with hi_p = n_pairs - p * n_pairs / kPasses
+    int p = 0, hi = n_pairs, lo = n_pairs - n_pairs / kPasses, base = 0;
+    while (p < kPasses - 1 && w >= base + (hi - lo) * n_bh) {
+      base += (hi - lo) * n_bh;
+      ++p;
+      hi = lo;
+      lo = (p == kPasses - 1) ? 0 : n_pairs - (p + 1) * n_pairs / kPasses;
+    }
+    const int width = hi - lo;
+    bh = (w - base) / width;
+    mp = hi - 1 - ((w - base) - bh * width);
+  } else {
+    bh = w / n_pairs;
+    mp = n_pairs - 1 - (w - bh * n_pairs);  // longest pair of the head first
+  }
   it.b = bh / a.Hq;
   it.h = bh - it.b * a.Hq;
+  (void)n_bh;
   it.hk = it.h / (a.Hq / a.Hkv);
   it.row0 = mp * (QT * BM);
   int kv_len = a.Skv;
@@ -403,10 +427,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = ptx::mbar_wait(&ctl->s_full[t], (cnt + j) & 1, abort_flag);
         if (!ok) break;
         if (j == 0) TT_STAMP(2);
+        TT_FINE(0);
         ptx::tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) ptx::tmem_ld32p(tS + cc * 32, s + cc * 32);
         ptx::tmem_wait_ld();
+        TT_FINE(1);
 
         const int col0 = j * BN;
         const bool mask_tile = (col0 + BN > kv_len) || (a.causal && col0 + BN - 1 > tile_row0);
@@ -467,14 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int e2 = 0; e2 < 64; e2 += 2) {
               const int e = hf * 64 + e2;
               float2 x = ptx::fma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nm2);
-              // kPolyNum of every kPolyDen pairs take their exponential on the FMA
-              // pipe, the rest on the special-function unit.
-              float2 p;
-              if ((e2 >> 1) % kPolyDen < kPolyNum) {
-                p = ptx::ex2_poly2(x);
-              } else {
-                p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
-              }
+              const float2 p = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
               lt = ptx::add2(lt, p);
               pk[e2 >> 1] = pack2<BF16>(p.x, p.y);
             }
@@ -490,9 +509,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           need_max = true;
         }
+        TT_FINE(2);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(&ctl->p_full[t]);
+        TT_FINE(3);
       }
       cnt += n_t;
       TT_STAMP(3);

@@ -321,45 +321,10 @@ __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;"
-      : "=l"(d)
-      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
-  return *reinterpret_cast<float2*>(&d);
-}
-// a + b rounded toward minus infinity (used to take floor() through a magic constant).
-__device__ __forceinline__ float2 add2_rm(float2 a, float2 b) {
-  uint64_t d;
-  asm("add.rm.f32x2 %0, %1, %2;"
-      : "=l"(d)
-      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
-  return *reinterpret_cast<float2*>(&d);
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-
-// 2^x for a pair of finite or -inf inputs, on the FMA pipe instead of the special-
-// function unit: x = n + f with n = floor(x), 2^f by a cubic fitted on [0, 1]
-// (p(0) = 1 exactly, relative error < 9e-5), 2^n by placing n + 127 in the exponent
-// field.  floor() comes from adding 1.5 * 2^23 + 127 with round-down: the sum's low
-// mantissa bits then hold n + 127.  Inputs below -126 are clamped (result 2^-126).
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  const float kMagic = 12582912.f + 127.f;
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 y = add2_rm(x, make_float2(kMagic, kMagic));
-  const float2 n = add2(y, make_float2(-kMagic, -kMagic));
-  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = fma2(f, make_float2(0.07706470787525177f, 0.07706470787525177f),
-                  make_float2(0.2276475429534912f, 0.2276475429534912f));
-  p = fma2(p, f, make_float2(0.6951162219047546f, 0.6951162219047546f));
-  p = fma2(p, f, make_float2(1.f, 1.f));
-  const float2 sc = make_float2(__uint_as_float(__float_as_uint(y.x) << 23), __uint_as_float(__float_as_uint(y.y) << 23));
-  return mul2(p, sc);
 }
 
 __device__ __forceinline__ float ex2(float x) {
