@@ -105,7 +105,11 @@ size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int 
   if (B <= 0 || Hq <= 0 || D <= 0) return 0;
   // fp16 / bf16 forward: one work counter for the persistent kernel's scheduler
   if (kind == TT_ATTN_KIND_FWD) return dtype == TT_ATTN_F32 ? 0 : 256;
-  if (kind == TT_ATTN_KIND_BWD) return round256(static_cast<size_t>(B) * Hq * (Lq > 0 ? Lq : 0) * sizeof(float));
+  if (kind == TT_ATTN_KIND_BWD) {
+    // delta [B,Hq,Lq] fp32; the fp16 / bf16 path adds an fp32 dQ accumulator [B,Hq,Lq,D]
+    const size_t rows = static_cast<size_t>(B) * Hq * (Lq > 0 ? Lq : 0);
+    return round256(rows * sizeof(float)) + (dtype == TT_ATTN_F32 ? 0 : round256(rows * D * sizeof(float)));
+  }
   if (kind == TT_ATTN_KIND_DECODE) {
     if (Skv <= 0) return 0;
     int nsplit, chunk;
@@ -183,7 +187,11 @@ int tt_attn_bwd(const tt_attn_bwd_params* p) {
   const size_t need = tt_attn_workspace_bytes(TT_ATTN_KIND_BWD, p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D);
   if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
   a.delta = static_cast<float*>(ws.ptr);
-  cudaError_t e = launch_bwd_simt(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
+  a.dq_accum = reinterpret_cast<float*>(static_cast<char*>(ws.ptr) +
+                                        round256(static_cast<size_t>(p->B) * p->Hq * p->Lq * sizeof(float)));
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  cudaError_t e = p->dtype == TT_ATTN_F32 ? launch_bwd_simt(p->dtype, p->D, a, stream)
+                                          : launch_bwd_tc(p->dtype, p->D, a, p->device, stream);
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
 

@@ -291,7 +291,21 @@ cudaError_t launch_t(const BwdArgs& a, cudaStream_t stream) {
   return e;
 }
 
+template <typename T, int D>
+cudaError_t launch_delta_t(const BwdArgs& a, cudaStream_t stream) {
+  const int64_t rows = static_cast<int64_t>(a.B) * a.Hq * a.Lq;
+  bwd_delta_kernel<T, D><<<static_cast<unsigned>((rows + 7) / 8), kThreads, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
 }  // namespace
+
+cudaError_t launch_bwd_delta(int dtype, int D, const BwdArgs& a, cudaStream_t stream) {
+  if (dtype == TT_ATTN_F32) return D == 64 ? launch_delta_t<float, 64>(a, stream) : launch_delta_t<float, 128>(a, stream);
+  if (dtype == TT_ATTN_F16)
+    return D == 64 ? launch_delta_t<__half, 64>(a, stream) : launch_delta_t<__half, 128>(a, stream);
+  return D == 64 ? launch_delta_t<__nv_bfloat16, 64>(a, stream) : launch_delta_t<__nv_bfloat16, 128>(a, stream);
+}
 
 cudaError_t launch_bwd_simt(int dtype, int D, const BwdArgs& a, cudaStream_t stream) {
   if (dtype == TT_ATTN_F32) return D == 64 ? launch_t<float, 64>(a, stream) : launch_t<float, 128>(a, stream);

@@ -1,0 +1,423 @@
+// Attention backward for fp16 / bf16 on sm_100a tensor cores.
+//
+// Supplies the gradient that FuncSDPAttention::backward leaves unimplemented
+// (reference: src/Function/FuncNNLayer.h:267); it equals the reference's chain
+// linear -> mul -> add -> softmax -> linear (src/Function/FuncNNLayer.h:20-34,
+// src/Function/FuncElemWise.h:77-87,113-123, src/Operation/OpNNLayerCpu.h:78-109):
+//   P  = exp(scale * Q K^T - LSE)          dP = dO V^T
+//   dS = P o (dP - delta) * scale          delta = rowsum(dO o O)
+//   dV = P^T dO      dK = dS^T Q      dQ = dS K
+//
+// One CTA owns a 128-row key tile of one (batch, kv head) and walks the query
+// tiles that see it (and the query heads of its group).  Everything is kept
+// TRANSPOSED so that a TMEM lane is a key row:
+//   S^T  = K Q^T   (SS MMA, both operands K-major)         -> TMEM region A
+//   dP^T = V dO^T  (SS MMA)                                -> TMEM region B
+//   the 128 compute threads (thread r = key row r) read S^T and dP^T, form
+//   P^T and dS^T with the per-query LSE / delta vectors from shared memory, and
+//   write them back as packed 16-bit pairs over regions A and B; dS^T also goes
+//   to shared memory
+//   dV  += P^T dO    (A = P^T from TMEM,  B = dO tile, MN-major)
+//   dK  += dS^T Q    (A = dS^T from TMEM, B = Q tile,  MN-major)
+//   dQ   = dS K      (A = dS^T tile in shared memory read MN-major, i.e. as dS;
+//                     B = K tile read MN-major)             -> TMEM region A
+// dV and dK accumulate in TMEM over the whole walk and are written once.  dQ of a
+// (key tile, query tile) pair is added to an fp32 buffer with red.global.add and
+// converted to the tensor dtype by a second small kernel.  Warp 4 feeds the tiles
+// with TMA (128-byte swizzle, no multicast), one thread of warp 5 issues the MMAs;
+// every wait is bounded.
+#include <type_traits>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tma_host.cuh"
+
+namespace ttattn {
+namespace {
+
+constexpr int BM = 128;  // key rows per CTA (= TMEM lanes)
+constexpr int BQ = 128;  // query rows per step
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-row tile
+
+struct __align__(8) SmemCtl {
+  uint64_t kv_full;
+  uint64_t q_full[2], q_empty[2];
+  uint64_t sp_full, pds_full, dq_full, a_free, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D>
+struct Cfg {
+  static constexpr int TB = BM * D * 2;            // bytes of one tile
+  static constexpr int NQ = (D == 64) ? 2 : 1;     // Q / dO ring depth (shared memory bound)
+  static constexpr int kDsBytes = BM * BQ * 2;     // dS^T tile
+  static constexpr int kVecBytes = 2 * 2 * BQ * 4; // lse / delta vectors, double buffered
+  static constexpr int kSmem = 2 * TB + 2 * NQ * TB + kDsBytes + kVecBytes + 1024 + 256;
+};
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+    bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                  const BwdArgs a) {
+  using C = Cfg<D>;
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  constexpr int TB = C::TB, NQ = C::NQ, HALVES = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TB;
+  uint8_t* sQ = sV + TB;          // NQ tiles
+  uint8_t* sdO = sQ + NQ * TB;    // NQ tiles
+  uint8_t* sdS = sdO + NQ * TB;   // dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
+  float* svec = reinterpret_cast<float*>(sdS + C::kDsBytes);  // [2 buffers][lse2 | delta][128]
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(reinterpret_cast<uint8_t*>(svec) + C::kVecBytes);
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // key tiles near the start see the most query tiles under the causal mask: launch them first
+  const int nt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = a.Hq / a.Hkv;
+  const int kv0 = nt * BM;
+  int kv_len = a.Skv;
+  if (a.kv_lens) {
+    int l = a.kv_lens[b];
+    kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
+  }
+  const int n_q_tiles = (a.Lq + BQ - 1) / BQ;
+  const int qt_begin = a.causal ? nt : 0;  // BM == BQ: query tiles before the key tile see none of it
+  const int per_head = (kv0 < kv_len && qt_begin < n_q_tiles) ? n_q_tiles - qt_begin : 0;
+  const int n_steps = per_head * group;
+
+  if (warp == 4 && lane == 0) {
+    ptx::mbar_init(&ctl->kv_full, 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&ctl->q_full[i], 1);
+      ptx::mbar_init(&ctl->q_empty[i], 1);
+    }
+    ptx::mbar_init(&ctl->sp_full, 1);
+    ptx::mbar_init(&ctl->pds_full, BM);
+    ptx::mbar_init(&ctl->dq_full, 1);
+    ptx::mbar_init(&ctl->a_free, BM);
+    ptx::mbar_init(&ctl->acc_full, 1);
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::tma_prefetch_desc(&tmQ);
+    ptx::tma_prefetch_desc(&tmK);
+    ptx::tma_prefetch_desc(&tmV);
+    ptx::tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 5) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs, cols [0,64)) -> dQ
+  const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
+  const uint32_t tdV = tmem + 256;       // D columns
+  const uint32_t tdK = tmem + 256 + D;   // D columns
+
+  if (warp == 4) {
+    // -------------------------------------------------------------- producer --
+    if (lane == 0 && n_steps > 0) {
+      ptx::mbar_arrive_expect_tx(&ctl->kv_full, 2 * TB);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf) {
+        ptx::tma_load_4d(sK + hf * kHalfBytes, &tmK, &ctl->kv_full, hf * 64, kv0, hk, b);
+        ptx::tma_load_4d(sV + hf * kHalfBytes, &tmV, &ctl->kv_full, hf * 64, kv0, hk, b);
+      }
+      for (int n = 0; n < n_steps; ++n) {
+        const int st = n % NQ;
+        const uint32_t ph = (n / NQ) & 1;
+        const int h = hk * group + n / per_head;
+        const int q0 = (qt_begin + n % per_head) * BQ;
+        if (!ptx::mbar_wait(&ctl->q_empty[st], ph ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(&ctl->q_full[st], 2 * TB);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) {
+          ptx::tma_load_4d(sQ + st * TB + hf * kHalfBytes, &tmQ, &ctl->q_full[st], hf * 64, q0, h, b);
+          ptx::tma_load_4d(sdO + st * TB + hf * kHalfBytes, &tmdO, &ctl->q_full[st], hf * 64, q0, h, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- issuer --
+    if (lane == 0 && n_steps > 0) {
+      constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
+      const uint32_t fmt = BF16 ? 1 : 0;
+      const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ, fmt, 0, 0);   // S^T, dP^T: N = queries
+      const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);  // dV, dK: A from TMEM, B MN-major
+      const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);   // dQ: both operands MN-major
+      const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
+      const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
+      const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK), kHalfBytes);
+      const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS), kHalfBytes);
+      bool ok = ptx::mbar_wait(&ctl->kv_full, 0, abort_flag);
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int st = n % NQ;
+        const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), 16);
+        const uint32_t dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), 16);
+        const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), kHalfBytes);
+        const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), kHalfBytes);
+        if (!(ok = ptx::mbar_wait(&ctl->q_full[st], (n / NQ) & 1, abort_flag))) break;
+        // region A still holds the previous step's dQ until the compute threads have read it
+        if (n > 0 && !(ok = ptx::mbar_wait(&ctl->a_free, (n - 1) & 1, abort_flag))) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+          ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+          ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+        }
+        ptx::mma_commit(&ctl->sp_full);
+        if (!(ok = ptx::mbar_wait(&ctl->pds_full, n & 1, abort_flag))) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks) {  // contraction over the 128 queries, 16 per step = 2048 bytes of B
+          ptx::mma_ts2(tdV, tA + ks * 8, dolo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks) {
+          ptx::mma_ts2(tdK, tB + ks * 8, qlo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
+          ptx::mma_ss2(tA, dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+        }
+        ptx::mma_commit(&ctl->dq_full);
+        ptx::mma_commit(&ctl->q_empty[st]);
+      }
+      if (ok) ptx::mma_commit(&ctl->acc_full);
+    }
+  } else {
+    // --------------------------------------------------------------- compute --
+    const int r = tid;  // key row within the tile (phase 1) / query row within the step (dQ read-out)
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int kv_row = kv0 + r;
+    const bool row_valid = kv_row < kv_len;
+    const float c = a.scale * kLog2e;
+    bool ok = true;
+
+    // per-query vectors of step n live in svec[(n & 1)]: [0,128) lse * log2(e), [128,256) delta
+    auto load_vec = [&](int n, float& lse2, float& dl) {
+      const int h = hk * group + n / per_head;
+      const int q = (qt_begin + n % per_head) * BQ + r;
+      lse2 = INFINITY;  // rows beyond Lq: P = 2^(x - inf) = 0
+      dl = 0.f;
+      if (q < a.Lq) {
+        const int64_t idx = (static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q;
+        lse2 = a.lse[idx] * kLog2e;
+        dl = a.delta[idx];
+      }
+    };
+    if (n_steps > 0) {
+      float l0, d0;
+      load_vec(0, l0, d0);
+      svec[r] = l0;
+      svec[BQ + r] = d0;
+    }
+    for (int n = 0; n < n_steps; ++n) {
+      const int h = hk * group + n / per_head;
+      const int q0 = (qt_begin + n % per_head) * BQ;
+      const float* vec = svec + (n & 1) * 2 * BQ;
+      float ln = 0.f, dn = 0.f;
+      if (n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
+      // all threads reach this point every step, expired waits included
+      ptx::named_barrier(1, BM);  // this step's vectors are in shared memory
+      if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
+      ptx::tc_fence_after();
+      const bool diag = a.causal && q0 < kv0 + BM;  // some (query, key) pairs of this step are masked
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t s[32], dp[32];
+        ptx::tmem_ld32(tA + lane_addr + cc * 32, s);
+        ptx::tmem_ld32(tB + lane_addr + cc * 32, dp);
+        ptx::tmem_wait_ld();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(vec + cc * 32 + i);
+          const float4 d4 = *reinterpret_cast<const float4*>(vec + BQ + cc * 32 + i);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float p[4], ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int q = q0 + cc * 32 + i + u;
+            const bool keep = row_valid && (!diag || q >= kv_row);
+            p[u] = keep ? ptx::ex2(fmaf(__uint_as_float(s[i + u]), c, -lv[u])) : 0.f;
+            ds[u] = p[u] * (__uint_as_float(dp[i + u]) - dv[u]) * a.scale;
+          }
+          pk[(i >> 1) + 0] = pack2<BF16>(p[0], p[1]);
+          pk[(i >> 1) + 1] = pack2<BF16>(p[2], p[3]);
+          dk[(i >> 1) + 0] = pack2<BF16>(ds[0], ds[1]);
+          dk[(i >> 1) + 1] = pack2<BF16>(ds[2], ds[3]);
+        }
+        ptx::tmem_st16(tA + lane_addr + cc * 16, pk);
+        ptx::tmem_st16(tB + lane_addr + cc * 16, dk);
+        // dS^T row r, queries [cc*32, cc*32+32): four 16-byte chunks of the 64-query block cc/2
+        uint8_t* row = sdS + (cc >> 1) * kHalfBytes + r * 128;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = (cc & 1) * 4 + ch;
+          *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
+        }
+      }
+      ptx::tmem_wait_st();
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&ctl->pds_full);
+      if (n + 1 < n_steps) {
+        float* nv = svec + ((n + 1) & 1) * 2 * BQ;
+        nv[r] = ln;
+        nv[BQ + r] = dn;
+      }
+
+      // dQ of this (key tile, query step): thread r now owns query row q0 + r
+      if (ok) ok = ptx::mbar_wait(&ctl->dq_full, n & 1, abort_flag);
+      ptx::tc_fence_after();
+      float* dq_row = a.dq_accum + ((static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q0 + r) * D;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t v[32];
+        ptx::tmem_ld32(tA + lane_addr + cc * 32, v);
+        ptx::tmem_wait_ld();
+        if (ok && q0 + r < a.Lq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            atomicAdd(reinterpret_cast<float4*>(dq_row + cc * 32 + i),
+                      make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                                  __uint_as_float(v[i + 3])));
+        }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&ctl->a_free);
+    }
+
+    // dV, dK of this key tile
+    T* dv_row = a.dv ? reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s
+                     : nullptr;
+    T* dk_row = a.dk ? reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s
+                     : nullptr;
+    if (n_steps > 0) {
+      if (ok) ok = ptx::mbar_wait(&ctl->acc_full, 0, abort_flag);
+      ptx::tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        T* out = which == 0 ? dv_row : dk_row;
+        const uint32_t src = (which == 0 ? tdV : tdK) + lane_addr;
+#pragma unroll 1
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t v[32];
+          ptx::tmem_ld32(src + cc * 32, v);
+          ptx::tmem_wait_ld();
+          if (ok && out && kv_row < a.Skv) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+              w.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              w.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+              w.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+              *reinterpret_cast<uint4*>(out + cc * 32 + i) = w;
+            }
+          }
+        }
+      }
+    } else if (kv_row < a.Skv) {
+      // no query sees this key tile: zero gradients
+#pragma unroll
+      for (int i = 0; i < D; i += 8) {
+        if (dv_row) *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
+        if (dk_row) *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+  if (tid == 0 && ctl->abort_flag && a.status) atomicOr(a.status, kStatusWaitExpired);
+}
+
+// dq_accum (fp32, dense [B,Hq,Lq,D]) -> dq (tensor dtype, strided)
+template <typename T, int D>
+__global__ void __launch_bounds__(256) dq_convert_kernel(const BwdArgs a) {
+  const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c8 = static_cast<int>(idx % (D / 8));
+    const int64_t rowi = idx / (D / 8);
+    const int i = static_cast<int>(rowi % a.Lq);
+    const int h = static_cast<int>((rowi / a.Lq) % a.Hq);
+    const int b = static_cast<int>(rowi / (static_cast<int64_t>(a.Lq) * a.Hq));
+    const float4* src = reinterpret_cast<const float4*>(a.dq_accum + rowi * D + c8 * 8);
+    const float4 x = src[0], y = src[1];
+    T out[8] = {from_f32<T>(x.x), from_f32<T>(x.y), from_f32<T>(x.z), from_f32<T>(x.w),
+                from_f32<T>(y.x), from_f32<T>(y.y), from_f32<T>(y.z), from_f32<T>(y.w)};
+    T* dst = reinterpret_cast<T*>(a.dq) + b * a.dqs.b + h * a.dqs.h + static_cast<int64_t>(i) * a.dqs.s + c8 * 8;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(out);
+  }
+}
+
+template <int D, bool BF16>
+cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t stream) {
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_map(&tq, dtype, a.q, D, a.Lq, a.Hq, a.B, a.qs) || !make_map(&tk, dtype, a.k, D, a.Skv, a.Hkv, a.B, a.ks) ||
+      !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs) ||
+      !make_map(&tdo, dtype, a.d_o, D, a.Lq, a.Hq, a.B, a.dos))
+    return cudaErrorInvalidValue;
+  const size_t acc_bytes = static_cast<size_t>(a.B) * a.Hq * a.Lq * D * sizeof(float);
+  cudaError_t e = cudaMemsetAsync(a.dq_accum, 0, acc_bytes, stream);
+  if (e != cudaSuccess) return e;
+  auto kern = bwd_tc_kernel<D, BF16>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((a.Skv + BM - 1) / BM, a.Hkv, a.B);
+  kern<<<grid, kThreads, Cfg<D>::kSmem, stream>>>(tq, tk, tv, tdo, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || !a.dq) return e;
+  const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
+  const int blocks = static_cast<int>((total + 255) / 256 < 8 * sm_count(device) ? (total + 255) / 256 : 8 * sm_count(device));
+  dq_convert_kernel<T, D><<<blocks, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream) {
+  cudaError_t e = launch_bwd_delta(dtype, D, a, stream);
+  if (e != cudaSuccess) return e;
+  const bool bf = dtype == TT_ATTN_BF16;
+  if (D == 128) return bf ? launch_t<128, true>(a, dtype, device, stream) : launch_t<128, false>(a, dtype, device, stream);
+  if (D == 64) return bf ? launch_t<64, true>(a, dtype, device, stream) : launch_t<64, false>(a, dtype, device, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace ttattn

@@ -47,7 +47,8 @@ struct BwdArgs {
   const void* o;
   const void* d_o;
   const float* lse;
-  float* delta;  // workspace [B, Hq, Lq]
+  float* delta;     // workspace [B, Hq, Lq]
+  float* dq_accum;  // workspace [B, Hq, Lq, D] fp32 (tensor-core path), zeroed by the launcher
   void* dq;
   void* dk;
   void* dv;
@@ -77,6 +78,10 @@ struct DecodeArgs {
 cudaError_t launch_fwd_tc(int dtype, int D, const FwdArgs& a, int device, cudaStream_t stream);
 cudaError_t launch_fwd_simt(int dtype, int D, const FwdArgs& a, cudaStream_t stream);
 cudaError_t launch_bwd_simt(int dtype, int D, const BwdArgs& a, cudaStream_t stream);
+// rowsum(dO o O) into a.delta only (first step of every backward)
+cudaError_t launch_bwd_delta(int dtype, int D, const BwdArgs& a, cudaStream_t stream);
+// fp16 / bf16 backward on the tensor cores; needs a.delta and a.dq_accum
+cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream);
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
 
 cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, int device, cudaStream_t stream,
