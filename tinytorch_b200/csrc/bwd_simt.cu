@@ -59,22 +59,32 @@ __device__ __forceinline__ void tile_nt(const float* A, const float* B, int ty, 
   }
 }
 
+// delta[b,h,i] = sum_d dO[i,d] * O[i,d].  Each thread reads 16 bytes of a row of
+// O and of dO; the D*sizeof(T)/16 threads of a row reduce with shuffles.
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const BwdArgs a) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + warp;
+  constexpr int N = 16 / sizeof(T);  // elements per thread
+  constexpr int TPR = D / N;         // threads per row (8, 16 or 32)
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
   const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq;
-  if (row >= total) return;
-  const int i = static_cast<int>(row % a.Lq);
-  const int h = static_cast<int>((row / a.Lq) % a.Hq);
-  const int b = static_cast<int>(row / (static_cast<int64_t>(a.Lq) * a.Hq));
-  const T* o = reinterpret_cast<const T*>(a.o) + b * a.os.b + h * a.os.h + i * a.os.s;
-  const T* g = reinterpret_cast<const T*>(a.d_o) + b * a.dos.b + h * a.dos.h + i * a.dos.s;
   float s = 0.f;
-  for (int d = lane; d < D; d += 32) s = fmaf(to_f32<T>(o[d]), to_f32<T>(g[d]), s);
+  if (row < total) {
+    const int i = static_cast<int>(row % a.Lq);
+    const int h = static_cast<int>((row / a.Lq) % a.Hq);
+    const int b = static_cast<int>(row / (static_cast<int64_t>(a.Lq) * a.Hq));
+    const T* o = reinterpret_cast<const T*>(a.o) + b * a.os.b + h * a.os.h + static_cast<int64_t>(i) * a.os.s + part * N;
+    const T* g =
+        reinterpret_cast<const T*>(a.d_o) + b * a.dos.b + h * a.dos.h + static_cast<int64_t>(i) * a.dos.s + part * N;
+    const uint4 ov = *reinterpret_cast<const uint4*>(o), gv = *reinterpret_cast<const uint4*>(g);
+    const T* op = reinterpret_cast<const T*>(&ov);
+    const T* gp = reinterpret_cast<const T*>(&gv);
 #pragma unroll
-  for (int of = 16; of >= 1; of >>= 1) s += __shfl_xor_sync(0xffffffffu, s, of);
-  if (lane == 0) a.delta[row] = s;
+    for (int e = 0; e < N; ++e) s = fmaf(to_f32<T>(op[e]), to_f32<T>(gp[e]), s);
+  }
+#pragma unroll
+  for (int of = TPR / 2; of >= 1; of >>= 1) s += __shfl_xor_sync(0xffffffffu, s, of);
+  if (part == 0 && row < total) a.delta[row] = s;
 }
 
 // Computes P and dS for the (query tile, key tile) pair held in shared memory and
@@ -268,7 +278,7 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdArgs a) {
 template <typename T, int D>
 cudaError_t launch_t(const BwdArgs& a, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.Hq * a.Lq;
-  bwd_delta_kernel<T, D><<<static_cast<unsigned>((rows + 7) / 8), kThreads, 0, stream>>>(a);
+  bwd_delta_kernel<T, D><<<static_cast<unsigned>((rows * (D * sizeof(T) / 16) + kThreads - 1) / kThreads), kThreads, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (a.dk || a.dv) {
@@ -294,7 +304,7 @@ cudaError_t launch_t(const BwdArgs& a, cudaStream_t stream) {
 template <typename T, int D>
 cudaError_t launch_delta_t(const BwdArgs& a, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.Hq * a.Lq;
-  bwd_delta_kernel<T, D><<<static_cast<unsigned>((rows + 7) / 8), kThreads, 0, stream>>>(a);
+  bwd_delta_kernel<T, D><<<static_cast<unsigned>((rows * (D * sizeof(T) / 16) + kThreads - 1) / kThreads), kThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

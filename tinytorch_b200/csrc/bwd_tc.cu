@@ -13,18 +13,19 @@
 // TRANSPOSED so that a TMEM lane is a key row:
 //   S^T  = K Q^T   (SS MMA, both operands K-major)         -> TMEM region A
 //   dP^T = V dO^T  (SS MMA)                                -> TMEM region B
-//   the 128 compute threads (thread r = key row r) read S^T and dP^T, form
-//   P^T and dS^T with the per-query LSE / delta vectors from shared memory, and
-//   write them back as packed 16-bit pairs over regions A and B; dS^T also goes
-//   to shared memory
+//   two compute warpgroups (thread r of each = key row r; warpgroup w takes
+//   queries [64w, 64w+64) of the step) read S^T and dP^T, form P^T and dS^T with
+//   the per-query LSE / delta vectors from shared memory, and write them back as
+//   packed 16-bit pairs over regions A and B; dS^T also goes to shared memory
 //   dV  += P^T dO    (A = P^T from TMEM,  B = dO tile, MN-major)
 //   dK  += dS^T Q    (A = dS^T from TMEM, B = Q tile,  MN-major)
 //   dQ   = dS K      (A = dS^T tile in shared memory read MN-major, i.e. as dS;
-//                     B = K tile read MN-major)             -> TMEM region A
+//                     B = K tile read MN-major)             -> its own TMEM columns
+//                     when D = 64, else region A
 // dV and dK accumulate in TMEM over the whole walk and are written once.  dQ of a
 // (key tile, query tile) pair is added to an fp32 buffer with red.global.add and
-// converted to the tensor dtype by a second small kernel.  Warp 4 feeds the tiles
-// with TMA (128-byte swizzle, no multicast), one thread of warp 5 issues the MMAs;
+// converted to the tensor dtype by a second small kernel.  Warp 8 feeds the tiles
+// with TMA (128-byte swizzle, no multicast), one thread of warp 9 issues the MMAs;
 // every wait is bounded.
 #include <type_traits>
 
@@ -37,7 +38,8 @@ namespace {
 
 constexpr int BM = 128;  // key rows per CTA (= TMEM lanes)
 constexpr int BQ = 128;  // query rows per step
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // two compute warpgroups (64 queries of every step each) + producer warp + issuer warp
+constexpr int kCompute = 256;
 constexpr int kTmemCols = 512;
 constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-row tile
 
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int per_head = (kv0 < kv_len && qt_begin < n_q_tiles) ? n_q_tiles - qt_begin : 0;
   const int n_steps = per_head * group;
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     ptx::mbar_init(&ctl->kv_full, 1);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -111,9 +113,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::mbar_init(&ctl->q_empty[i], 1);
     }
     ptx::mbar_init(&ctl->sp_full, 1);
-    ptx::mbar_init(&ctl->pds_full, BM);
+    ptx::mbar_init(&ctl->pds_full, kCompute);
     ptx::mbar_init(&ctl->dq_full, 1);
-    ptx::mbar_init(&ctl->a_free, BM);
+    ptx::mbar_init(&ctl->a_free, kCompute);
     ptx::mbar_init(&ctl->acc_full, 1);
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tma_prefetch_desc(&tmV);
     ptx::tma_prefetch_desc(&tmdO);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -130,12 +132,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs, cols [0,64)) -> dQ
+  const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs in cols [0,32) and [64,96)) -> dQ (D = 128)
   const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
   const uint32_t tdV = tmem + 256;       // D columns
   const uint32_t tdK = tmem + 256 + D;   // D columns
+  // dQ of a step: with D = 64 there is room for columns of its own, so the next
+  // step's S^T / dP^T need not wait for the read-out; with D = 128 it reuses region A
+  constexpr bool kDqOwn = (D == 64);
+  const uint32_t tdQ = kDqOwn ? tmem + 384 : tA;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // -------------------------------------------------------------- producer --
     if (lane == 0 && n_steps > 0) {
       ptx::mbar_arrive_expect_tx(&ctl->kv_full, 2 * TB);
@@ -158,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- issuer --
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
@@ -178,8 +184,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), kHalfBytes);
         const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), kHalfBytes);
         if (!(ok = ptx::mbar_wait(&ctl->q_full[st], (n / NQ) & 1, abort_flag))) break;
-        // region A still holds the previous step's dQ until the compute threads have read it
-        if (n > 0 && !(ok = ptx::mbar_wait(&ctl->a_free, (n - 1) & 1, abort_flag))) break;
+        // without columns of its own, the previous step's dQ occupies region A until read
+        if (!kDqOwn && n > 0 && !(ok = ptx::mbar_wait(&ctl->a_free, (n - 1) & 1, abort_flag))) break;
         ptx::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -193,18 +199,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ptx::mma_commit(&ctl->sp_full);
         if (!(ok = ptx::mbar_wait(&ctl->pds_full, n & 1, abort_flag))) break;
+        if (kDqOwn && n > 0 && !(ok = ptx::mbar_wait(&ctl->a_free, (n - 1) & 1, abort_flag))) break;
         ptx::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {  // contraction over the 128 queries, 16 per step = 2048 bytes of B
-          ptx::mma_ts2(tdV, tA + ks * 8, dolo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
+          ptx::mma_ts2(tdV, tA + (ks >> 2) * 64 + (ks & 3) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+                       (n > 0 || ks > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {
-          ptx::mma_ts2(tdK, tB + ks * 8, qlo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
+          ptx::mma_ts2(tdK, tB + (ks >> 2) * 64 + (ks & 3) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+                       (n > 0 || ks > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
-          ptx::mma_ss2(tA, dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+          ptx::mma_ss2(tdQ, dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
         }
         ptx::mma_commit(&ctl->dq_full);
         ptx::mma_commit(&ctl->q_empty[st]);
@@ -213,14 +222,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // --------------------------------------------------------------- compute --
-    const int r = tid;  // key row within the tile (phase 1) / query row within the step (dQ read-out)
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int wg = warp >> 2;   // which 64 queries of every step
+    const int r = tid & (BM - 1);  // key row within the tile (phase 1) / query row of the step (dQ read-out)
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int kv_row = kv0 + r;
     const bool row_valid = kv_row < kv_len;
     const float c = a.scale * kLog2e;
     bool ok = true;
 
-    // per-query vectors of step n live in svec[(n & 1)]: [0,128) lse * log2(e), [128,256) delta
+    // per-query vectors of step n live in svec[(n & 1)]: [0,128) lse * log2(e), [128,256) delta;
+    // warpgroup 0 fetches them one step ahead
     auto load_vec = [&](int n, float& lse2, float& dl) {
       const int h = hk * group + n / per_head;
       const int q = (qt_begin + n % per_head) * BQ + r;
@@ -232,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         dl = a.delta[idx];
       }
     };
-    if (n_steps > 0) {
+    if (n_steps > 0 && wg == 0) {
       float l0, d0;
       load_vec(0, l0, d0);
       svec[r] = l0;
@@ -243,14 +254,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int q0 = (qt_begin + n % per_head) * BQ;
       const float* vec = svec + (n & 1) * 2 * BQ;
       float ln = 0.f, dn = 0.f;
-      if (n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
+      if (wg == 0 && n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
       // all threads reach this point every step, expired waits included
-      ptx::named_barrier(1, BM);  // this step's vectors are in shared memory
+      ptx::named_barrier(1, kCompute);  // this step's vectors are in shared memory
       if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
       ptx::tc_fence_after();
       const bool diag = a.causal && q0 < kv0 + BM;  // some (query, key) pairs of this step are masked
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        const int cc = wg * 2 + c2;  // 32-query chunk of the step
         uint32_t s[32], dp[32];
         ptx::tmem_ld32(tA + lane_addr + cc * 32, s);
         ptx::tmem_ld32(tB + lane_addr + cc * 32, dp);
@@ -274,8 +286,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           dk[(i >> 1) + 0] = pack2<BF16>(ds[0], ds[1]);
           dk[(i >> 1) + 1] = pack2<BF16>(ds[2], ds[3]);
         }
-        ptx::tmem_st16(tA + lane_addr + cc * 16, pk);
-        ptx::tmem_st16(tB + lane_addr + cc * 16, dk);
+        // Warpgroup w keeps its 16-bit results in columns [64w, 64w+32) of the
+        // region, i.e. over the first chunk it loaded itself, never over columns
+        // the other warpgroup still has to read.
+        ptx::tmem_st16(tA + lane_addr + wg * 64 + c2 * 16, pk);
+        ptx::tmem_st16(tB + lane_addr + wg * 64 + c2 * 16, dk);
         // dS^T row r, queries [cc*32, cc*32+32): four 16-byte chunks of the 64-query block cc/2
         uint8_t* row = sdS + (cc >> 1) * kHalfBytes + r * 128;
 #pragma unroll
@@ -289,22 +304,27 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&ctl->pds_full);
-      if (n + 1 < n_steps) {
+      if (wg == 0 && n + 1 < n_steps) {
         float* nv = svec + ((n + 1) & 1) * 2 * BQ;
         nv[r] = ln;
         nv[BQ + r] = dn;
       }
 
-      // dQ of this (key tile, query step): thread r now owns query row q0 + r
+      // dQ of this (key tile, query step): thread r now owns query row q0 + r and
+      // warpgroup w the columns [w*D/2, (w+1)*D/2)
       if (ok) ok = ptx::mbar_wait(&ctl->dq_full, n & 1, abort_flag);
       ptx::tc_fence_after();
-      float* dq_row = a.dq_accum + ((static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q0 + r) * D;
-#pragma unroll 1
-      for (int cc = 0; cc < D / 32; ++cc) {
+      float* dq_row = a.dq_accum + ((static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q0 + r) * D + wg * (D / 2);
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
         uint32_t v[32];
-        ptx::tmem_ld32(tA + lane_addr + cc * 32, v);
+        ptx::tmem_ld32(tdQ + lane_addr + wg * (D / 2) + cc * 32, v);
         ptx::tmem_wait_ld();
+#ifdef TT_EXPERIMENT_NO_DQ_RED
+        if (false) {
+#else
         if (ok && q0 + r < a.Lq) {
+#endif
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             atomicAdd(reinterpret_cast<float4*>(dq_row + cc * 32 + i),
@@ -316,49 +336,43 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::mbar_arrive(&ctl->a_free);
     }
 
-    // dV, dK of this key tile
-    T* dv_row = a.dv ? reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s
-                     : nullptr;
-    T* dk_row = a.dk ? reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s
-                     : nullptr;
+    // dV (warpgroup 0) and dK (warpgroup 1) of this key tile
+    T* out = nullptr;
+    if (wg == 0 && a.dv)
+      out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
+    if (wg == 1 && a.dk)
+      out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
     if (n_steps > 0) {
       if (ok) ok = ptx::mbar_wait(&ctl->acc_full, 0, abort_flag);
       ptx::tc_fence_after();
+      const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        T* out = which == 0 ? dv_row : dk_row;
-        const uint32_t src = (which == 0 ? tdV : tdK) + lane_addr;
-#pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t v[32];
-          ptx::tmem_ld32(src + cc * 32, v);
-          ptx::tmem_wait_ld();
-          if (ok && out && kv_row < a.Skv) {
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t v[32];
+        ptx::tmem_ld32(src + cc * 32, v);
+        ptx::tmem_wait_ld();
+        if (ok && out && kv_row < a.Skv) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-              w.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-              w.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-              w.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-              *reinterpret_cast<uint4*>(out + cc * 32 + i) = w;
-            }
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+            w.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            w.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+            w.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+            *reinterpret_cast<uint4*>(out + cc * 32 + i) = w;
           }
         }
       }
-    } else if (kv_row < a.Skv) {
+    } else if (out && kv_row < a.Skv) {
       // no query sees this key tile: zero gradients
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
-        if (dv_row) *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
-        if (dk_row) *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
-      }
+      for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(out + i) = make_uint4(0, 0, 0, 0);
     }
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
