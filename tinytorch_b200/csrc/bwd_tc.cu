@@ -46,7 +46,8 @@ constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-ro
 struct __align__(8) SmemCtl {
   uint64_t kv_full;
   uint64_t q_full[2], q_empty[2];
-  uint64_t sp_full, pds_full, dq_full, a_free, acc_full;
+  uint64_t sp_full, pds_full, acc_full;
+  uint64_t dq_full[2], dq_free[2];  // per dQ buffer
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -54,11 +55,32 @@ struct __align__(8) SmemCtl {
 template <int D>
 struct Cfg {
   static constexpr int TB = BM * D * 2;            // bytes of one tile
-  static constexpr int NQ = (D == 64) ? 2 : 1;     // Q / dO ring depth (shared memory bound)
-  static constexpr int kDsBytes = BM * BQ * 2;     // dS^T tile
+  // With D = 64 there is room (TMEM columns and shared memory) to overlap the
+  // steps: two dQ accumulators, two dS^T tiles, two Q / dO stages, and dQ leaves
+  // through a staging tile and TMA reductions.  With D = 128 the steps run one
+  // after the other and dQ is added with red.global.
+  static constexpr bool kPipe = (D == 64);
+  static constexpr int NQ = kPipe ? 2 : 1;         // Q / dO ring depth
+  static constexpr int NDS = kPipe ? 2 : 1;        // dS^T tiles
+  static constexpr int kDsBytes = BM * BQ * 2;     // one dS^T tile
+  static constexpr int kDqStage = kPipe ? 2 * BQ * 128 : 0;  // two boxes of 128 rows x 32 floats
   static constexpr int kVecBytes = 2 * 2 * BQ * 4; // lse / delta vectors, double buffered
-  static constexpr int kSmem = 2 * TB + 2 * NQ * TB + kDsBytes + kVecBytes + 1024 + 256;
+  static constexpr int kSmem = 2 * TB + 2 * NQ * TB + NDS * kDsBytes + kDqStage + kVecBytes + 1024 + 256;
 };
+
+// Developer aid, compiled out by default: with -DTT_ATTN_PROFILE the first CTA
+// writes clock64() stamps per step to the buffer passed as `status`
+// (int64 [3 = warpgroup 0, warpgroup 1, issuer][32 steps][8 slots]).
+#ifdef TT_ATTN_PROFILE
+#define TT_BSTAMP(who, slot)                                                        \
+  do {                                                                              \
+    if (prof && n < 32) prof[((who)*32 + n) * 8 + (slot)] = clock64();             \
+  } while (0)
+#else
+#define TT_BSTAMP(who, slot) \
+  do {                       \
+  } while (0)
+#endif
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -75,18 +97,20 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
     bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                  const BwdArgs a) {
+                  const __grid_constant__ CUtensorMap tmdQ, const BwdArgs a) {
   using C = Cfg<D>;
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   constexpr int TB = C::TB, NQ = C::NQ, HALVES = D / 64;
+  constexpr bool kPipe = C::kPipe;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + TB;
   uint8_t* sQ = sV + TB;          // NQ tiles
   uint8_t* sdO = sQ + NQ * TB;    // NQ tiles
-  uint8_t* sdS = sdO + NQ * TB;   // dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
-  float* svec = reinterpret_cast<float*>(sdS + C::kDsBytes);  // [2 buffers][lse2 | delta][128]
+  uint8_t* sdS = sdO + NQ * TB;   // NDS x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
+  uint8_t* sdq = sdS + C::NDS * C::kDsBytes;  // dQ staging (kPipe): per warpgroup [128 queries][32 floats], swizzled
+  float* svec = reinterpret_cast<float*>(sdq + C::kDqStage);  // [2 buffers][lse2 | delta][128]
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(reinterpret_cast<uint8_t*>(svec) + C::kVecBytes);
   volatile int* abort_flag = &ctl->abort_flag;
 
@@ -114,15 +138,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     ptx::mbar_init(&ctl->sp_full, 1);
     ptx::mbar_init(&ctl->pds_full, kCompute);
-    ptx::mbar_init(&ctl->dq_full, 1);
-    ptx::mbar_init(&ctl->a_free, kCompute);
     ptx::mbar_init(&ctl->acc_full, 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&ctl->dq_full[i], 1);
+      ptx::mbar_init(&ctl->dq_free[i], kCompute);
+    }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);
     ptx::tma_prefetch_desc(&tmK);
     ptx::tma_prefetch_desc(&tmV);
     ptx::tma_prefetch_desc(&tmdO);
+    if (kPipe) ptx::tma_prefetch_desc(&tmdQ);
   }
   if (warp == 9) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -132,14 +160,19 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
+#ifdef TT_ATTN_PROFILE
+  long long* prof = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9) &&
+                     a.status)
+                        ? reinterpret_cast<long long*>(a.status)
+                        : nullptr;
+#endif
   const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs in cols [0,32) and [64,96)) -> dQ (D = 128)
   const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
   const uint32_t tdV = tmem + 256;       // D columns
   const uint32_t tdK = tmem + 256 + D;   // D columns
-  // dQ of a step: with D = 64 there is room for columns of its own, so the next
-  // step's S^T / dP^T need not wait for the read-out; with D = 128 it reuses region A
-  constexpr bool kDqOwn = (D == 64);
-  const uint32_t tdQ = kDqOwn ? tmem + 384 : tA;
+  // dQ of step n: two buffers of D columns when there is room (D = 64), so that the
+  // read-out of one step overlaps the MMAs of the next; else region A is reused
+  auto tdQ = [&](int n) { return kPipe ? tmem + 384 + (n & 1) * D : tA; };
 
   if (warp == 8) {
     // -------------------------------------------------------------- producer --
@@ -175,18 +208,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
       const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
       const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK), kHalfBytes);
-      const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS), kHalfBytes);
       bool ok = ptx::mbar_wait(&ctl->kv_full, 0, abort_flag);
-      for (int n = 0; n < n_steps && ok; ++n) {
-        const int st = n % NQ;
-        const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), 16);
-        const uint32_t dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), 16);
-        const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), kHalfBytes);
-        const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), kHalfBytes);
-        if (!(ok = ptx::mbar_wait(&ctl->q_full[st], (n / NQ) & 1, abort_flag))) break;
-        // without columns of its own, the previous step's dQ occupies region A until read
-        if (!kDqOwn && n > 0 && !(ok = ptx::mbar_wait(&ctl->a_free, (n - 1) & 1, abort_flag))) break;
+      auto stage_lo = [&](const uint8_t* base, int n, uint32_t lbo) {
+        return ptx::smem_desc_lo(ptx::smem_u32(base + (n % NQ) * TB), lbo);
+      };
+      // S^T = K Q^T and dP^T = V dO^T of step n
+      auto issue_s_dp = [&](int n) {
+        if (!ptx::mbar_wait(&ctl->q_full[n % NQ], (n / NQ) & 1, abort_flag)) return false;
         ptx::tc_fence_after();
+        const uint32_t qlo = stage_lo(sQ, n, 16), dolo = stage_lo(sdO, n, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
@@ -198,8 +228,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
         }
         ptx::mma_commit(&ctl->sp_full);
+        return true;
+      };
+      if (ok) ok = issue_s_dp(0);
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int st = n % NQ;
+        const uint32_t qlo_mn = stage_lo(sQ, n, kHalfBytes), dolo_mn = stage_lo(sdO, n, kHalfBytes);
+        const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (n % C::NDS) * C::kDsBytes), kHalfBytes);
         if (!(ok = ptx::mbar_wait(&ctl->pds_full, n & 1, abort_flag))) break;
-        if (kDqOwn && n > 0 && !(ok = ptx::mbar_wait(&ctl->a_free, (n - 1) & 1, abort_flag))) break;
         ptx::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {  // contraction over the 128 queries, 16 per step = 2048 bytes of B
@@ -211,12 +247,24 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ts2(tdK, tB + (ks >> 2) * 64 + (ks & 3) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
                        (n > 0 || ks > 0) ? 1u : 0u);
         }
+        if (kPipe) {
+          // P^T / dS^T of this step have been consumed from TMEM (in issue order):
+          // the next step's S^T / dP^T go first, then this step's dQ, which reads
+          // dS^T from shared memory
+          if (n + 1 < n_steps && !(ok = issue_s_dp(n + 1))) break;
+          if (n >= 2 && !(ok = ptx::mbar_wait(&ctl->dq_free[n & 1], ((n >> 1) - 1) & 1, abort_flag))) break;
+        }
 #pragma unroll
         for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
-          ptx::mma_ss2(tdQ, dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+          ptx::mma_ss2(tdQ(n), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
         }
-        ptx::mma_commit(&ctl->dq_full);
+        ptx::mma_commit(&ctl->dq_full[kPipe ? (n & 1) : 0]);
         ptx::mma_commit(&ctl->q_empty[st]);
+        if (!kPipe && n + 1 < n_steps) {
+          // region A holds this step's dQ until the compute threads have read it
+          if (!(ok = ptx::mbar_wait(&ctl->dq_free[0], n & 1, abort_flag))) break;
+          if (!(ok = issue_s_dp(n + 1))) break;
+        }
       }
       if (ok) ptx::mma_commit(&ctl->acc_full);
     }
@@ -249,15 +297,66 @@ __global__ void __launch_bounds__(kThreads, 1)
       svec[r] = l0;
       svec[BQ + r] = d0;
     }
-    for (int n = 0; n < n_steps; ++n) {
+    // dQ of step n -> global; thread r owns query row q0 + r, warpgroup w the
+    // columns [w*D/2, (w+1)*D/2)
+    auto read_out_dq = [&](int n) {
       const int h = hk * group + n / per_head;
       const int q0 = (qt_begin + n % per_head) * BQ;
+      const int buf = kPipe ? (n & 1) : 0;
+      if (ok) ok = ptx::mbar_wait(&ctl->dq_full[buf], (kPipe ? (n >> 1) : n) & 1, abort_flag);
+      ptx::tc_fence_after();
+      if constexpr (kPipe) {
+        // through a swizzled staging tile and one TMA reduction per warpgroup
+        // (coalesced; rows beyond Lq are clipped by the tensor map)
+        uint32_t v[32];
+        ptx::tmem_ld32(tdQ(n) + lane_addr + wg * 32, v);
+        ptx::tmem_wait_ld();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->dq_free[buf]);
+        uint8_t* stage = sdq + wg * (BQ * 128);
+        if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging tile
+        ptx::named_barrier(3 + wg, BM);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
+              make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+        ptx::fence_proxy_async_smem();
+        ptx::named_barrier(3 + wg, BM);
+        if (r == 0 && ok) {
+          ptx::tma_reduce_add_4d(&tmdQ, stage, wg * 32, q0, h, b);
+          ptx::bulk_commit();
+        }
+      } else {
+        float* dq_row = a.dq_accum + ((static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q0 + r) * D + wg * (D / 2);
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) {
+          uint32_t v[32];
+          ptx::tmem_ld32(tdQ(n) + lane_addr + wg * (D / 2) + cc * 32, v);
+          ptx::tmem_wait_ld();
+          if (ok && q0 + r < a.Lq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              atomicAdd(reinterpret_cast<float4*>(dq_row + cc * 32 + i),
+                        make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                                    __uint_as_float(v[i + 3])));
+          }
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->dq_free[0]);
+      }
+    };
+
+    for (int n = 0; n < n_steps; ++n) {
+      const int q0 = (qt_begin + n % per_head) * BQ;
       const float* vec = svec + (n & 1) * 2 * BQ;
+      uint8_t* ds_tile = sdS + (n % C::NDS) * C::kDsBytes;
       float ln = 0.f, dn = 0.f;
       if (wg == 0 && n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
       // all threads reach this point every step, expired waits included
+      TT_BSTAMP(wg, 0);
       ptx::named_barrier(1, kCompute);  // this step's vectors are in shared memory
       if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
+      TT_BSTAMP(wg, 2);
       ptx::tc_fence_after();
       const bool diag = a.causal && q0 < kv0 + BM;  // some (query, key) pairs of this step are masked
 #pragma unroll
@@ -292,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tmem_st16(tA + lane_addr + wg * 64 + c2 * 16, pk);
         ptx::tmem_st16(tB + lane_addr + wg * 64 + c2 * 16, dk);
         // dS^T row r, queries [cc*32, cc*32+32): four 16-byte chunks of the 64-query block cc/2
-        uint8_t* row = sdS + (cc >> 1) * kHalfBytes + r * 128;
+        uint8_t* row = ds_tile + (cc >> 1) * kHalfBytes + r * 128;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           const int chunk = (cc & 1) * 4 + ch;
@@ -300,40 +399,28 @@ __global__ void __launch_bounds__(kThreads, 1)
               make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
         }
       }
+      TT_BSTAMP(wg, 3);
       ptx::tmem_wait_st();
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&ctl->pds_full);
+      TT_BSTAMP(wg, 4);
       if (wg == 0 && n + 1 < n_steps) {
         float* nv = svec + ((n + 1) & 1) * 2 * BQ;
         nv[r] = ln;
         nv[BQ + r] = dn;
       }
-
-      // dQ of this (key tile, query step): thread r now owns query row q0 + r and
-      // warpgroup w the columns [w*D/2, (w+1)*D/2)
-      if (ok) ok = ptx::mbar_wait(&ctl->dq_full, n & 1, abort_flag);
-      ptx::tc_fence_after();
-      float* dq_row = a.dq_accum + ((static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q0 + r) * D + wg * (D / 2);
-#pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        uint32_t v[32];
-        ptx::tmem_ld32(tdQ + lane_addr + wg * (D / 2) + cc * 32, v);
-        ptx::tmem_wait_ld();
-#ifdef TT_EXPERIMENT_NO_DQ_RED
-        if (false) {
-#else
-        if (ok && q0 + r < a.Lq) {
-#endif
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            atomicAdd(reinterpret_cast<float4*>(dq_row + cc * 32 + i),
-                      make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                                  __uint_as_float(v[i + 3])));
-        }
+      // dQ: of the previous step while this step's MMAs run (kPipe), else of this step
+      if (kPipe) {
+        if (n >= 1) read_out_dq(n - 1);
+      } else {
+        read_out_dq(n);
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(&ctl->a_free);
+      TT_BSTAMP(wg, 6);
+    }
+    if (kPipe && n_steps > 0) {
+      read_out_dq(n_steps - 1);
+      if (r == 0) ptx::bulk_wait_all();
     }
 
     // dV (warpgroup 0) and dK (warpgroup 1) of this key tile
@@ -402,10 +489,11 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const BwdArgs a) {
 template <int D, bool BF16>
 cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t stream) {
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   if (!make_map(&tq, dtype, a.q, D, a.Lq, a.Hq, a.B, a.qs) || !make_map(&tk, dtype, a.k, D, a.Skv, a.Hkv, a.B, a.ks) ||
       !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs) ||
-      !make_map(&tdo, dtype, a.d_o, D, a.Lq, a.Hq, a.B, a.dos))
+      !make_map(&tdo, dtype, a.d_o, D, a.Lq, a.Hq, a.B, a.dos) ||
+      !make_map_f32(&tdq, a.dq_accum, D, a.Lq, a.Hq, a.B))
     return cudaErrorInvalidValue;
   const size_t acc_bytes = static_cast<size_t>(a.B) * a.Hq * a.Lq * D * sizeof(float);
   cudaError_t e = cudaMemsetAsync(a.dq_accum, 0, acc_bytes, stream);
@@ -414,7 +502,7 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
   if (e != cudaSuccess) return e;
   dim3 grid((a.Skv + BM - 1) / BM, a.Hkv, a.B);
-  kern<<<grid, kThreads, Cfg<D>::kSmem, stream>>>(tq, tk, tv, tdo, a);
+  kern<<<grid, kThreads, Cfg<D>::kSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   e = cudaGetLastError();
   if (e != cudaSuccess || !a.dq) return e;
   const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
