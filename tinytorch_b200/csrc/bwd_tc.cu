@@ -13,8 +13,8 @@
 // TRANSPOSED so that a TMEM lane is a key row:
 //   S^T  = K Q^T   (SS MMA, both operands K-major)         -> TMEM region A
 //   dP^T = V dO^T  (SS MMA)                                -> TMEM region B
-//   two compute warpgroups (thread r of each = key row r; warpgroup w takes
-//   queries [64w, 64w+64) of the step) read S^T and dP^T, form P^T and dS^T with
+//   four compute warpgroups (thread r of each = key row r; warpgroup w takes
+//   queries [32w, 32w+32) of the step) read S^T and dP^T, form P^T and dS^T with
 //   the per-query LSE / delta vectors from shared memory, and write them back as
 //   packed 16-bit pairs over regions A and B; dS^T also goes to shared memory
 //   dV  += P^T dO    (A = P^T from TMEM,  B = dO tile, MN-major)
@@ -24,8 +24,8 @@
 //                     when D = 64, else region A
 // dV and dK accumulate in TMEM over the whole walk and are written once.  dQ of a
 // (key tile, query tile) pair is added to an fp32 buffer with red.global.add and
-// converted to the tensor dtype by a second small kernel.  Warp 8 feeds the tiles
-// with TMA (128-byte swizzle, no multicast), one thread of warp 9 issues the MMAs;
+// converted to the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
+// with TMA (128-byte swizzle, no multicast), one thread of warp 17 issues the MMAs;
 // every wait is bounded.
 #include <type_traits>
 
@@ -38,8 +38,9 @@ namespace {
 
 constexpr int BM = 128;  // key rows per CTA (= TMEM lanes)
 constexpr int BQ = 128;  // query rows per step
-constexpr int kThreads = 320;  // two compute warpgroups (64 queries of every step each) + producer warp + issuer warp
-constexpr int kCompute = 256;
+constexpr int kThreads = 576;  // four compute warpgroups (32 queries of every step each) + producer warp + issuer warp
+constexpr int kCompute = 512;
+constexpr int kReaders = 256;  // warpgroups 0 and 1 also move dQ, dV and dK out of TMEM
 constexpr int kTmemCols = 512;
 constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-row tile
 
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int per_head = (kv0 < kv_len && qt_begin < n_q_tiles) ? n_q_tiles - qt_begin : 0;
   const int n_steps = per_head * group;
 
-  if (warp == 8 && lane == 0) {
+  if (warp == 16 && lane == 0) {
     ptx::mbar_init(&ctl->kv_full, 1);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&ctl->dq_full[i], 1);
-      ptx::mbar_init(&ctl->dq_free[i], kCompute);
+      ptx::mbar_init(&ctl->dq_free[i], kReaders);
     }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tma_prefetch_desc(&tmdO);
     if (kPipe) ptx::tma_prefetch_desc(&tmdQ);
   }
-  if (warp == 9) {
+  if (warp == 17) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -161,12 +162,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
 #ifdef TT_ATTN_PROFILE
-  long long* prof = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9) &&
+  long long* prof = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 17) &&
                      a.status)
                         ? reinterpret_cast<long long*>(a.status)
                         : nullptr;
 #endif
-  const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs in cols [0,32) and [64,96)) -> dQ (D = 128)
+  const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w) -> dQ (D = 128)
   const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
   const uint32_t tdV = tmem + 256;       // D columns
   const uint32_t tdK = tmem + 256 + D;   // D columns
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // read-out of one step overlaps the MMAs of the next; else region A is reused
   auto tdQ = [&](int n) { return kPipe ? tmem + 384 + (n & 1) * D : tA; };
 
-  if (warp == 8) {
+  if (warp == 16) {
     // -------------------------------------------------------------- producer --
     if (lane == 0 && n_steps > 0) {
       ptx::mbar_arrive_expect_tx(&ctl->kv_full, 2 * TB);
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------------------------------------------------------- issuer --
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
@@ -239,12 +240,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {  // contraction over the 128 queries, 16 per step = 2048 bytes of B
-          ptx::mma_ts2(tdV, tA + (ks >> 2) * 64 + (ks & 3) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+          ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
                        (n > 0 || ks > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {
-          ptx::mma_ts2(tdK, tB + (ks >> 2) * 64 + (ks & 3) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+          ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
                        (n > 0 || ks > 0) ? 1u : 0u);
         }
         if (kPipe) {
@@ -270,25 +271,26 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // --------------------------------------------------------------- compute --
-    const int wg = warp >> 2;   // which 64 queries of every step
+    const int wg = warp >> 2;   // which 32 queries of every step
     const int r = tid & (BM - 1);  // key row within the tile (phase 1) / query row of the step (dQ read-out)
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int kv_row = kv0 + r;
     const bool row_valid = kv_row < kv_len;
     const float c = a.scale * kLog2e;
+    const float2 c2v = make_float2(c, c), sc2 = make_float2(a.scale, a.scale);
     bool ok = true;
 
-    // per-query vectors of step n live in svec[(n & 1)]: [0,128) lse * log2(e), [128,256) delta;
+    // per-query vectors of step n live in svec[(n & 1)]: [0,128) -lse * log2(e), [128,256) -delta * scale;
     // warpgroup 0 fetches them one step ahead
     auto load_vec = [&](int n, float& lse2, float& dl) {
       const int h = hk * group + n / per_head;
       const int q = (qt_begin + n % per_head) * BQ + r;
-      lse2 = INFINITY;  // rows beyond Lq: P = 2^(x - inf) = 0
+      lse2 = -INFINITY;  // rows beyond Lq: P = 2^(x - inf) = 0
       dl = 0.f;
       if (q < a.Lq) {
         const int64_t idx = (static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q;
-        lse2 = a.lse[idx] * kLog2e;
-        dl = a.delta[idx];
+        lse2 = -a.lse[idx] * kLog2e;
+        dl = -a.delta[idx] * a.scale;
       }
     };
     if (n_steps > 0 && wg == 0) {
@@ -359,42 +361,52 @@ __global__ void __launch_bounds__(kThreads, 1)
       TT_BSTAMP(wg, 2);
       ptx::tc_fence_after();
       const bool diag = a.causal && q0 < kv0 + BM;  // some (query, key) pairs of this step are masked
+      const bool masked = diag || kv0 + BM > kv_len;
 #pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        const int cc = wg * 2 + c2;  // 32-query chunk of the step
-        uint32_t s[32], dp[32];
-        ptx::tmem_ld32(tA + lane_addr + cc * 32, s);
-        ptx::tmem_ld32(tB + lane_addr + cc * 32, dp);
+      for (int sc = 0; sc < 2; ++sc) {
+        const int col = wg * 32 + sc * 16;  // 16 queries of the step
+        uint32_t s[16], dp[16];
+        ptx::tmem_ld16(tA + lane_addr + col, s);
+        ptx::tmem_ld16(tB + lane_addr + col, dp);
         ptx::tmem_wait_ld();
-        uint32_t pk[16], dk[16];
+        uint32_t pk[8], dk[8];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(vec + cc * 32 + i);
-          const float4 d4 = *reinterpret_cast<const float4*>(vec + BQ + cc * 32 + i);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float p[4], ds[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int q = q0 + cc * 32 + i + u;
-            const bool keep = row_valid && (!diag || q >= kv_row);
-            p[u] = keep ? ptx::ex2(fmaf(__uint_as_float(s[i + u]), c, -lv[u])) : 0.f;
-            ds[u] = p[u] * (__uint_as_float(dp[i + u]) - dv[u]) * a.scale;
+        for (int i = 0; i < 16; i += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(vec + col + i);
+          const float4 d4 = *reinterpret_cast<const float4*>(vec + BQ + col + i);
+          // P = 2^(c*s - lse2), dS = P * (scale*dP - scale*delta), in packed fp32 pairs
+          float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v,
+                                make_float2(l4.x, l4.y));
+          float2 x1 = ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v,
+                                make_float2(l4.z, l4.w));
+          float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), ptx::ex2(x1.y));
+          if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
+            const int q = q0 + col + i;
+            if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
+            if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
+            if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
+            if (!row_valid || (diag && q + 3 < kv_row)) p1.y = 0.f;
           }
-          pk[(i >> 1) + 0] = pack2<BF16>(p[0], p[1]);
-          pk[(i >> 1) + 1] = pack2<BF16>(p[2], p[3]);
-          dk[(i >> 1) + 0] = pack2<BF16>(ds[0], ds[1]);
-          dk[(i >> 1) + 1] = pack2<BF16>(ds[2], ds[3]);
+          const float2 g0 = ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2,
+                                      make_float2(d4.x, d4.y));
+          const float2 g1 = ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2,
+                                      make_float2(d4.z, d4.w));
+          const float2 ds0 = ptx::mul2(p0, g0), ds1 = ptx::mul2(p1, g1);
+          pk[(i >> 1) + 0] = pack2<BF16>(p0.x, p0.y);
+          pk[(i >> 1) + 1] = pack2<BF16>(p1.x, p1.y);
+          dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
+          dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
         }
-        // Warpgroup w keeps its 16-bit results in columns [64w, 64w+32) of the
-        // region, i.e. over the first chunk it loaded itself, never over columns
-        // the other warpgroup still has to read.
-        ptx::tmem_st16(tA + lane_addr + wg * 64 + c2 * 16, pk);
-        ptx::tmem_st16(tB + lane_addr + wg * 64 + c2 * 16, dk);
-        // dS^T row r, queries [cc*32, cc*32+32): four 16-byte chunks of the 64-query block cc/2
-        uint8_t* row = ds_tile + (cc >> 1) * kHalfBytes + r * 128;
+        // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the
+        // region, i.e. over the first 16 columns it loaded itself, never over
+        // columns another warpgroup still has to read.
+        ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
+        ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
+        // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
+        uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int chunk = (cc & 1) * 4 + ch;
+        for (int ch = 0; ch < 2; ++ch) {
+          const int chunk = ((col & 63) >> 3) + ch;
           *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
               make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
         }
@@ -411,14 +423,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         nv[BQ + r] = dn;
       }
       // dQ: of the previous step while this step's MMAs run (kPipe), else of this step
-      if (kPipe) {
-        if (n >= 1) read_out_dq(n - 1);
-      } else {
-        read_out_dq(n);
+      if (wg < 2) {
+        if (kPipe) {
+          if (n >= 1) read_out_dq(n - 1);
+        } else {
+          read_out_dq(n);
+        }
       }
       TT_BSTAMP(wg, 6);
     }
-    if (kPipe && n_steps > 0) {
+    if (kPipe && n_steps > 0 && wg < 2) {
       read_out_dq(n_steps - 1);
       if (r == 0) ptx::bulk_wait_all();
     }
@@ -429,7 +443,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
     if (wg == 1 && a.dk)
       out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
-    if (n_steps > 0) {
+    if (wg >= 2) {
+      // warpgroups 2 and 3 have nothing to write
+    } else if (n_steps > 0) {
       if (ok) ok = ptx::mbar_wait(&ctl->acc_full, 0, abort_flag);
       ptx::tc_fence_after();
       const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
@@ -459,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
