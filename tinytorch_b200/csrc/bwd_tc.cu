@@ -25,7 +25,7 @@
 // dV and dK accumulate in TMEM over the whole walk and are written once.  dQ of a
 // (key tile, query tile) pair is added to an fp32 buffer with red.global.add and
 // converted to the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
-// with TMA (128-byte swizzle, no multicast), one thread of warp 17 issues the MMAs;
+// with TMA (128-byte swizzle, one copy per CTA), one thread of warp 17 issues the MMAs;
 // every wait is bounded.
 #include <type_traits>
 

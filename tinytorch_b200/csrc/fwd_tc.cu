@@ -10,7 +10,7 @@
 // first, so that the CTAs running at any moment share few heads' K/V in L2 and
 // the last items to be drawn are the shortest.
 //   warp 8   producer : draws items and publishes them to the other warps; TMA
-//                       tiled loads (128-byte swizzle, no multicast) of the item's
+//                       tiled loads (128-byte swizzle, one copy per CTA) of the item's
 //                       two Q tiles and of each K and V tile into a 2-stage ring.
 //                       It runs ahead: the next item's Q and first K/V tiles are
 //                       requested while the current item is still being computed.

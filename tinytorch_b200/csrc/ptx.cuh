@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use:
-// mbarrier, TMA tiled loads (never cluster-multicast), tcgen05 MMA / TMEM.
+// mbarrier, TMA tiled loads (each CTA fetches its own copy), tcgen05 MMA / TMEM.
 // Every wait helper here is bounded: on expiry it returns false and the caller
 // unwinds; nothing in this file can spin forever.
 #pragma once
@@ -86,7 +86,7 @@ __device__ __forceinline__ void tc_fence_after() {
 }
 
 // ------------------------------------------------------------------ TMA -----
-// 4-D tiled load global -> shared, completion on an mbarrier.  No multicast.
+// 4-D tiled load global -> shared, completion on an mbarrier; CTA-local destination only.
 // c0 is the innermost coordinate; c0 * element size must be a multiple of 16 B.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             int c2, int c3) {
