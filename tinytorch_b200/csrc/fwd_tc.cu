@@ -107,37 +107,12 @@ struct Item {
   int b, h, hk, row0, kv_len, nt0, nt1, n_max;
 };
 
-// Item order.  Under the causal mask a pair of query tiles costs in proportion
-// to its position, so pairs are dealt in kPasses passes over the heads: the latest
-// (longest) quarter of every head first, the earliest (shortest) quarter last, and
-// within a pass head by head, longest pair first.  CTAs running at the same time
-// then share few heads' K/V in L2, and the items drawn last, which decide how long
-// the other SMs idle at the end, are the shortest ones.
-constexpr int kPasses = 4;
-
 __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs) {
   Item it;
-  const int n_bh = a.Hq * a.B;
-  int bh, mp;
-  if (n_pairs >= 2 * kPasses) {
-    // pass p covers pairs [lo_p, hi_p) with hi_p = n_pairs - p * n_pairs / kPasses
-    int p = 0, hi = n_pairs, lo = n_pairs - n_pairs / kPasses, base = 0;
-    while (p < kPasses - 1 && w >= base + (hi - lo) * n_bh) {
-      base += (hi - lo) * n_bh;
-      ++p;
-      hi = lo;
-      lo = (p == kPasses - 1) ? 0 : n_pairs - (p + 1) * n_pairs / kPasses;
-    }
-    const int width = hi - lo;
-    bh = (w - base) / width;
-    mp = hi - 1 - ((w - base) - bh * width);
-  } else {
-    bh = w / n_pairs;
-    mp = n_pairs - 1 - (w - bh * n_pairs);  // longest pair of the head first
-  }
+  const int bh = w / n_pairs;
+  const int mp = n_pairs - 1 - (w - bh * n_pairs);  // longest pair of the head first
   it.b = bh / a.Hq;
   it.h = bh - it.b * a.Hq;
-  (void)n_bh;
   it.hk = it.h / (a.Hq / a.Hkv);
   it.row0 = mp * (QT * BM);
   int kv_len = a.Skv;
