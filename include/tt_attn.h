@@ -16,8 +16,19 @@
  *  - dtype uses the reference's enum values (src/Tensor/DType.h:20-24):
  *    0 = Float32, 1 = Float16, 2 = BFloat16.  Q, K, V, O (and dO, dQ, dK, dV)
  *    share one dtype.  Accumulation is always fp32.  LSE is fp32.
- *  - is_causal keeps key j for query i iff j <= i, top-left aligned for any
+ *  - is_causal = 1 keeps key j for query i iff j <= i, top-left aligned for any
  *    Lq, Skv (src/Function/FuncNNLayer.h:243-246, src/Operation/OpTransformCpu.h:204).
+ *    is_causal = 2 (no counterpart in the reference) aligns the triangle to the
+ *    bottom right instead: j <= i + (len_b - Lq) with len_b = kv_lens[b] or Skv,
+ *    which is what a chunk of Lq new queries at the end of a cache of len_b keys needs.
+ *  - mask (optional, prefill forward and backward) is the reference's attnMask
+ *    (src/Function/FuncNNLayer.h:249-256): a boolean mask (one byte per element,
+ *    non-zero = the key participates) or an additive mask added to the scaled
+ *    scores, broadcast against [B, Hq, Lq, Skv].  The key dimension is contiguous;
+ *    the strides of (b, h, l) are given in elements and 0 broadcasts that
+ *    dimension.  The mask receives no gradient.  It may be combined with
+ *    is_causal and kv_lens (the reference allows only one of mask / isCausal,
+ *    src/Function/FuncNNLayer.h:242).
  *  - scale multiplies Q.K^T before the softmax; the caller passes 1/sqrt(D) when
  *    the user gave none (src/Function/FuncNNLayer.h:235).
  *  - kv_lens (optional, device int32 [B]): key j of batch b participates iff
@@ -55,7 +66,7 @@
 extern "C" {
 #endif
 
-#define TT_ATTN_ABI_VERSION 1
+#define TT_ATTN_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define TT_ATTN_API __attribute__((visibility("default")))
@@ -88,13 +99,22 @@ typedef struct tt_attn_alloc_hook {
   void* ctx;
 } tt_attn_alloc_hook;
 
+enum tt_attn_causal { TT_ATTN_CAUSAL_NONE = 0, TT_ATTN_CAUSAL_TOP_LEFT = 1, TT_ATTN_CAUSAL_BOTTOM_RIGHT = 2 };
+
+enum tt_attn_mask_kind {
+  TT_ATTN_MASK_NONE = 0,
+  TT_ATTN_MASK_BOOL = 1,    /* uint8, non-zero = participate (the reference's Bool tensor) */
+  TT_ATTN_MASK_ADD = 2,     /* additive, same dtype as q (the reference adds a mask of the tensors' dtype) */
+  TT_ATTN_MASK_ADD_F32 = 3  /* additive, fp32 */
+};
+
 /* Strides in elements of dimensions (b, h, s); D is contiguous. */
 typedef struct tt_attn_strides {
   int64_t b, h, s;
 } tt_attn_strides;
 
 /* Forward.  Replaces FuncSDPAttention::forward (src/Function/FuncNNLayer.h:231-266)
- * for dropoutP == 0 and a mask that is absent, causal, or a per-batch length. */
+ * for dropoutP == 0. */
 typedef struct tt_attn_fwd_params {
   uint32_t struct_size; /* sizeof(tt_attn_fwd_params) */
   int32_t dtype;
@@ -114,6 +134,12 @@ typedef struct tt_attn_fwd_params {
   size_t workspace_bytes;
   const tt_attn_alloc_hook* alloc;
   int32_t* status; /* device word, may be NULL */
+  /* fields below were added with TT_ATTN_ABI_VERSION 2; a caller compiled against
+   * version 1 passes the shorter struct_size and gets "no mask" */
+  const void* mask;        /* device pointer or NULL */
+  int32_t mask_kind;       /* tt_attn_mask_kind */
+  int32_t reserved0;       /* must be 0 */
+  int64_t mask_strides[3]; /* elements, for (b, h, l); 0 = broadcast; keys are contiguous */
 } tt_attn_fwd_params;
 
 /* Backward.  Supplies what FuncSDPAttention::backward (src/Function/FuncNNLayer.h:267)
@@ -146,6 +172,12 @@ typedef struct tt_attn_bwd_params {
   size_t workspace_bytes;
   const tt_attn_alloc_hook* alloc;
   int32_t* status;
+  /* fields below were added with TT_ATTN_ABI_VERSION 2; a caller compiled against
+   * version 1 passes the shorter struct_size and gets "no mask" */
+  const void* mask;        /* device pointer or NULL */
+  int32_t mask_kind;       /* tt_attn_mask_kind */
+  int32_t reserved0;       /* must be 0 */
+  int64_t mask_strides[3]; /* elements, for (b, h, l); 0 = broadcast; keys are contiguous */
 } tt_attn_bwd_params;
 
 /* Single-token decode: Lq == 1, one query per sequence against a KV cache

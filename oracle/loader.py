@@ -110,7 +110,7 @@ class Reference:
 
     def __init__(self):
         self.lib = C.CDLL(REF_SO)
-        for n in ("ref_sdpa_fwd", "ref_sdpa_grad", "ref_repeat_interleave", "ref_lse"):
+        for n in ("ref_sdpa_fwd", "ref_sdpa_grad", "ref_repeat_interleave", "ref_lse", "ref_sdpa_fwd_mask"):
             getattr(self.lib, n).restype = C.c_int
         i64 = C.c_int64
         self.lib.ref_sdpa_fwd.argtypes = [C.c_void_p] * 3 + [i64] * 5 + [C.c_int, C.c_void_p, C.c_float,
@@ -118,6 +118,8 @@ class Reference:
         self.lib.ref_sdpa_grad.argtypes = [C.c_void_p] * 4 + [i64] * 5 + [C.c_int, C.c_float] + [C.c_void_p] * 4
         self.lib.ref_repeat_interleave.argtypes = [C.c_void_p] + [i64] * 5 + [C.c_void_p]
         self.lib.ref_lse.argtypes = [C.c_void_p] * 2 + [i64] * 5 + [C.c_int, C.c_float, C.c_void_p]
+        self.lib.ref_sdpa_fwd_mask.argtypes = [C.c_void_p] * 3 + [i64] * 5 + [C.c_void_p, C.c_int, C.c_void_p,
+                                                                               C.c_float, C.c_void_p]
 
     def fwd(self, q, k, v, causal=False, scale=None, kv_lens=None):
         q, k, v = _f32(q), _f32(k), _f32(v)
@@ -130,6 +132,22 @@ class Reference:
         out = np.empty_like(q)
         self.lib.ref_sdpa_fwd(_ptr(q), _ptr(k), _ptr(v), B, H, L, S, D, int(causal), _ptr(mask),
                               float(scale) if scale is not None else 0.0, _ptr(out))
+        return out
+
+    def fwd_mask(self, q, k, v, mask, scale=None):
+        """sdpAttention(q, k, v, false, mask): bool mask (True = attend) or float mask (added),
+        any shape of up to 4 dimensions that broadcasts against [B, H, L, S]."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        B, H, L, D = q.shape
+        S = k.shape[2]
+        mask = np.asarray(mask)
+        m4 = mask.reshape((1,) * (4 - mask.ndim) + mask.shape)
+        is_float = m4.dtype != np.bool_
+        m4 = np.ascontiguousarray(m4.astype(np.float32 if is_float else np.uint8))
+        shape = (C.c_int64 * 4)(*m4.shape)
+        out = np.empty_like(q)
+        self.lib.ref_sdpa_fwd_mask(_ptr(q), _ptr(k), _ptr(v), B, H, L, S, D, _ptr(m4), int(is_float), shape,
+                                   float(scale) if scale is not None else 0.0, _ptr(out))
         return out
 
     def grad(self, q, k, v, dout, causal=False, scale=None):

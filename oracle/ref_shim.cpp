@@ -11,6 +11,8 @@
  *                           src/Function/FuncNNLayer.h:14-35,
  *                           src/Function/FuncElemWise.h:71-124,
  *                           src/Function/FuncActivation.h:42-63
+ *   ref_sdpa_fwd_mask       function::sdpAttention with an attnMask of any broadcastable
+ *                           shape, Bool or Float32      src/Function/FuncNNLayer.h:249-256
  *   ref_repeat_interleave   op::repeatInterleave        src/Operation/OpTransform.h:168
  *   ref_lse                 op::logSoftmax on the scaled, biased scores the
  *                           forward builds              src/Function/FuncNNLayer.h:237-260
@@ -130,6 +132,28 @@ int ref_lse(const float* q, const float* k, int64_t B, int64_t H, int64_t L, int
   return 0;
 }
 
-int ref_abi_version(void) { return 1; }
+/* sdpAttention(q, k, v, false, mask): mask is [m0,m1,m2,m3] (each extent 1 or the
+ * full one), uint8 (1 = attend) when is_float == 0, else float added to the scores. */
+int ref_sdpa_fwd_mask(const float* q, const float* k, const float* v, int64_t B, int64_t H, int64_t L, int64_t S,
+                      int64_t D, const void* mask, int is_float, const int64_t* mshape, float scale, float* out) {
+  NoGradGuard guard;
+  Tensor tq = fromHost(q, {B, H, L, D});
+  Tensor tk = fromHost(k, {B, H, S, D});
+  Tensor tv = fromHost(v, {B, H, S, D});
+  std::vector<int64_t> ms = {mshape[0], mshape[1], mshape[2], mshape[3]};
+  Tensor tm;
+  if (is_float) {
+    tm = fromHost(static_cast<const float*>(mask), ms);
+  } else {
+    tm = Tensor::empty(IntArrayView(ms), Options(Device(DeviceType::CPU), DType::Bool));
+    std::memcpy(tm.dataPtr<uint8_t>(), mask, static_cast<size_t>(tm.numel()));
+  }
+  std::optional<float> sc = scale > 0.f ? std::optional<float>(scale) : std::nullopt;
+  Tensor y = function::sdpAttention(tq, tk, tv, false, tm, 0.f, sc);
+  toHost(y, out);
+  return 0;
+}
+
+int ref_abi_version(void) { return 2; }
 
 }  // extern "C"

@@ -12,6 +12,8 @@ Outputs (both committed):
                            code computes for them here
   ref_seeded.npz           seeded inputs and the reference's outputs for small
                            causal fwd+bwd, length-masked decode and GQA cases
+  ref_seeded_mask.npz      the same for attnMask: a Bool mask [B,1,L,S] and a float
+                           mask [L,S] (src/Function/FuncNNLayer.h:249-256)
 """
 import json
 import os
@@ -82,6 +84,21 @@ def main():
     out.update(s_q=Q, s_k=K, s_v=V, s_scale=np.float32(0.3), s_o=ref.fwd(Q, K, V, scale=0.3),
                s_o_causal=ref.fwd(Q, K, V, causal=True, scale=0.3))
     np.savez_compressed(os.path.join(HERE, "ref_seeded.npz"), **out)
+
+    # --- attnMask through the reference's sdpAttention (its own generator, so that
+    # ref_seeded.npz stays byte-identical when this part changes)
+    rng = np.random.default_rng(20240608)
+    B, H, L, S, D = 2, 2, 72, 136, 64
+    Q = rng.standard_normal((B, H, L, D), dtype=np.float32)
+    K, V = (rng.standard_normal((B, H, S, D), dtype=np.float32) for _ in range(2))
+    mb = rng.random((B, 1, L, S)) < 0.6
+    mb[..., 0] = True  # no fully masked row (those are NaN in the reference)
+    mf = rng.standard_normal((L, S)).astype(np.float32)
+    mf[rng.random((L, S)) < 0.15] = -np.inf
+    mf[:, 0] = 0.25
+    np.savez_compressed(os.path.join(HERE, "ref_seeded_mask.npz"), q=Q, k=K, v=V, mask_bool=mb, mask_float=mf,
+                        o_bool=ref.fwd_mask(Q, K, V, mb), o_float=ref.fwd_mask(Q, K, V, mf),
+                        o_float_scale=ref.fwd_mask(Q, K, V, mf, scale=0.2))
     print("wrote", os.listdir(HERE))
 
 

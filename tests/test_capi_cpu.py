@@ -31,7 +31,7 @@ def test_exports_every_declared_symbol(lib):
 
 
 def test_version_and_strerror(lib):
-    assert lib.tt_attn_version() == 1
+    assert lib.tt_attn_version() == 2  # 2: mask fields and the bottom-right causal alignment
     assert lib.tt_attn_strerror(0) == b"ok"
     for code in range(-10, 0):
         assert b"unknown" not in lib.tt_attn_strerror(code)
@@ -65,10 +65,23 @@ def _fwd(**kw):
     (dict(k=0x1004), -5),
     (dict(q_strides=_capi.Strides(4096, 1024, 4)), -5),
     (dict(B=70000), -10),
+    (dict(is_causal=3), -3),
+    (dict(mask=0x2000, mask_kind=4), -2),
+    (dict(mask=None, mask_kind=1), -1),
 ])
 def test_fwd_rejects_bad_arguments(lib, kw, code):
     p = _fwd(**kw)
     assert lib.tt_attn_fwd(C.byref(p)) == code
+
+
+def test_version_1_struct_is_still_accepted(lib):
+    # a caller compiled against ABI version 1 passes the struct without the mask fields; it must get past
+    # the size check (and then fail on something else: here a misaligned pointer)
+    p = _fwd(k=0x1004)
+    p.struct_size = _capi.FwdParams.mask.offset
+    assert lib.tt_attn_fwd(C.byref(p)) == -5
+    p.struct_size = _capi.FwdParams.mask.offset + 8
+    assert lib.tt_attn_fwd(C.byref(p)) == -8
 
 
 def test_null_param_pointers(lib):

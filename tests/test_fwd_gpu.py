@@ -63,6 +63,32 @@ def test_tensor_core_shapes(oracle, dt, D, L, S, causal):
     assert np.abs(to_np(lse) - wl).max() <= 2e-3
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("which", ["few_rows", "all_rows"])
+def test_row_maximum_grows_in_later_key_tiles(oracle, dt, D, causal, which):
+    # The tensor-core kernel keeps a row's reference maximum across key tiles and only takes a new one
+    # (rescaling O and the running sum) when a tile's exponentials grow large.  Here late keys score far
+    # above the first tile's maximum: for a few rows of a warp only, or for every row.
+    B, H, L, S = 1, 2, 512, 512
+    rng = np.random.default_rng(21)
+    qn = (rng.standard_normal((B, H, L, D)) * 0.5).astype(np.float32)
+    kn = (rng.standard_normal((B, H, S, D)) * 0.5).astype(np.float32)
+    vn = rng.standard_normal((B, H, S, D)).astype(np.float32)
+    if which == "few_rows":
+        for row, key in ((300, 140), (305, 290), (420, 400), (511, 130)):
+            kn[:, :, key] = qn[:, :, row] * (1200.0 / D)   # score * scale of (row, key) around 25-50
+    else:
+        kn[:, :, 256:] *= 12.0
+        kn[:, :, 400:] *= 3.0
+    q, k, v = (torch.from_numpy(x).to(DTYPES[dt]).cuda() for x in (qn, kn, vn))
+    o, lse = _run(q, k, v, isCausal=causal)
+    wo, wl = oracle.fwd(*(to_np(t) for t in (q, k, v)), causal=causal)
+    assert np.abs(to_np(o) - wo).max() <= TOL_ABS_16BIT
+    assert np.abs(to_np(lse) - wl).max() <= 2e-2
+
+
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
 def test_kv_lens_and_scale(oracle, dt):
     B, H, L, S, D = 3, 2, 150, 300, 128

@@ -116,3 +116,33 @@ def test_threads_do_not_change_results(oracle):
     b, _ = oracle.fwd(q, k, v, causal=True)
     oracle.set_threads(n)
     assert np.array_equal(a, b)
+
+
+def _bias_of(mask):
+    mask = np.asarray(mask)
+    if mask.dtype == np.bool_:
+        return np.where(mask, np.float32(0), np.float32(-np.inf)).astype(np.float32)
+    return mask.astype(np.float32)
+
+
+def test_seeded_masks_bitexact(oracle):
+    # attnMask of the reference (src/Function/FuncNNLayer.h:249-256): Bool [B,1,L,S] and float [L,S]
+    g = np.load(os.path.join(GOLDEN, "ref_seeded_mask.npz"))
+    q, k, v = g["q"], g["k"], g["v"]
+    o, _ = oracle.fwd(q, k, v, bias=_bias_of(g["mask_bool"]))
+    assert np.array_equal(o, g["o_bool"])
+    o, _ = oracle.fwd(q, k, v, bias=_bias_of(g["mask_float"]))
+    assert np.array_equal(o, g["o_float"])
+    o, _ = oracle.fwd(q, k, v, bias=_bias_of(g["mask_float"]), scale=0.2)
+    assert np.array_equal(o, g["o_float_scale"])
+
+
+def test_masks_live_against_reference(oracle, reference):
+    rng = np.random.default_rng(77)
+    B, H, L, S, D = 1, 3, 33, 50, 64
+    q = rng.standard_normal((B, H, L, D), dtype=np.float32)
+    k, v = (rng.standard_normal((B, H, S, D), dtype=np.float32) for _ in range(2))
+    m = rng.random((1, H, L, S)) < 0.5
+    m[..., 0] = True
+    o, _ = oracle.fwd(q, k, v, bias=_bias_of(m))
+    assert np.array_equal(o, reference.fwd_mask(q, k, v, m))

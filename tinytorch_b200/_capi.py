@@ -12,6 +12,11 @@ LIB_PATH = os.environ.get("TT_ATTN_LIB") or os.path.join(HERE, "lib", "libtt_att
 
 F32, F16, BF16 = 0, 1, 2
 KIND_FWD, KIND_BWD, KIND_DECODE = 0, 1, 2
+CAUSAL_NONE, CAUSAL_TOP_LEFT, CAUSAL_BOTTOM_RIGHT = 0, 1, 2
+MASK_NONE, MASK_BOOL, MASK_ADD, MASK_ADD_F32 = 0, 1, 2, 3
+
+_MASK_FIELDS = [("mask", C.c_void_p), ("mask_kind", C.c_int32), ("reserved0", C.c_int32),
+                ("mask_strides", C.c_int64 * 3)]
 STATIC_SCRATCH_BYTES = 24 << 20  # TT_ATTN_STATIC_SCRATCH_BYTES
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_size_t, C.c_int)
@@ -38,7 +43,7 @@ class FwdParams(C.Structure):
         ("device", C.c_int32), ("stream", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("alloc", C.POINTER(AllocHook)), ("status", C.c_void_p),
-    ]
+    ] + _MASK_FIELDS
 
 
 class BwdParams(C.Structure):
@@ -55,7 +60,7 @@ class BwdParams(C.Structure):
         ("device", C.c_int32), ("stream", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("alloc", C.POINTER(AllocHook)), ("status", C.c_void_p),
-    ]
+    ] + _MASK_FIELDS
 
 
 class DecodeParams(C.Structure):

@@ -1,6 +1,7 @@
 // extern "C" entry points of libtt_attn.so: argument validation, workspace
 // handling through the caller's allocator hook, device guard, kernel dispatch.
 // See include/tt_attn.h for the contract of each function.
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 
@@ -100,6 +101,22 @@ const char* tt_attn_strerror(int status) {
   }
 }
 
+}  // extern "C"
+
+namespace {
+// Validates the optional mask of a prefill call.
+int take_mask(const void* ptr, int kind, const int64_t st[3], MaskArgs* m) {
+  *m = MaskArgs{};
+  if (kind == TT_ATTN_MASK_NONE || !ptr) return (kind == TT_ATTN_MASK_NONE) ? TT_ATTN_OK : TT_ATTN_ERR_NULL;
+  if (kind < 0 || kind > TT_ATTN_MASK_ADD_F32) return TT_ATTN_ERR_DTYPE;
+  if (st[0] < 0 || st[1] < 0 || st[2] < 0) return TT_ATTN_ERR_SHAPE;
+  m->ptr = ptr, m->kind = kind, m->sb = st[0], m->sh = st[1], m->sl = st[2];
+  return TT_ATTN_OK;
+}
+}  // namespace
+
+extern "C" {
+
 size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int Lq, int Skv, int D) {
   (void)Hkv;
   if (B <= 0 || Hq <= 0 || D <= 0) return 0;
@@ -122,7 +139,8 @@ size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int 
 
 int tt_attn_fwd(const tt_attn_fwd_params* p) {
   if (!p) return TT_ATTN_ERR_NULL;
-  if (p->struct_size != sizeof(tt_attn_fwd_params)) return TT_ATTN_ERR_STRUCT;
+  const bool v2 = p->struct_size == sizeof(tt_attn_fwd_params);
+  if (!v2 && p->struct_size != offsetof(tt_attn_fwd_params, mask)) return TT_ATTN_ERR_STRUCT;
   if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D)) return rc;
   if (!p->q || !p->k || !p->v || !p->o) return TT_ATTN_ERR_NULL;
   const size_t es = elem_size(p->dtype);
@@ -136,10 +154,13 @@ int tt_attn_fwd(const tt_attn_fwd_params* p) {
       !strides_ok(a.ks, es) || !strides_ok(a.vs, es) || !strides_ok(a.os, es))
     return TT_ATTN_ERR_ALIGN;
   a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.Lq = p->Lq, a.Skv = p->Skv;
-  a.causal = p->is_causal ? 1 : 0;
+  if (p->is_causal < 0 || p->is_causal > TT_ATTN_CAUSAL_BOTTOM_RIGHT) return TT_ATTN_ERR_SHAPE;
+  a.causal = p->is_causal;
   a.scale = p->scale;
   a.kv_lens = p->kv_lens;
   a.status = p->status;
+  if (v2)
+    if (int rc = take_mask(p->mask, p->mask_kind, p->mask_strides, &a.mask)) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;
@@ -154,7 +175,8 @@ int tt_attn_fwd(const tt_attn_fwd_params* p) {
 
 int tt_attn_bwd(const tt_attn_bwd_params* p) {
   if (!p) return TT_ATTN_ERR_NULL;
-  if (p->struct_size != sizeof(tt_attn_bwd_params)) return TT_ATTN_ERR_STRUCT;
+  const bool v2 = p->struct_size == sizeof(tt_attn_bwd_params);
+  if (!v2 && p->struct_size != offsetof(tt_attn_bwd_params, mask)) return TT_ATTN_ERR_STRUCT;
   if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, p->Lq, p->Skv, p->D)) return rc;
   if (!p->q || !p->k || !p->v || !p->o || !p->d_o || !p->lse) return TT_ATTN_ERR_NULL;
   if (!p->dq && !p->dk && !p->dv) return TT_ATTN_OK;
@@ -177,10 +199,13 @@ int tt_attn_bwd(const tt_attn_bwd_params* p) {
   for (const Str3* s : sts)
     if (!strides_ok(*s, es)) return TT_ATTN_ERR_ALIGN;
   a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.Lq = p->Lq, a.Skv = p->Skv;
-  a.causal = p->is_causal ? 1 : 0;
+  if (p->is_causal < 0 || p->is_causal > TT_ATTN_CAUSAL_BOTTOM_RIGHT) return TT_ATTN_ERR_SHAPE;
+  a.causal = p->is_causal;
   a.scale = p->scale;
   a.kv_lens = p->kv_lens;
   a.status = p->status;
+  if (v2)
+    if (int rc = take_mask(p->mask, p->mask_kind, p->mask_strides, &a.mask)) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;

@@ -89,10 +89,13 @@ __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const BwdArgs a) {
 
 // Computes P and dS for the (query tile, key tile) pair held in shared memory and
 // writes them to Ps / dSs ([row][col], leading dimension TN+1).
-template <int D>
+// `shift` is the causal alignment (key j participates iff j <= i + shift), `mask_base` the
+// mask offset of this (b, h).
+template <typename T, int D>
 __device__ __forceinline__ void tile_p_ds(const BwdArgs& a, const float* Qs, const float* Ks, const float* Vs,
                                           const float* dOs, const float* lse_s, const float* delta_s, float* Ps,
-                                          float* dSs, int row0, int col0, int kv_len, int ty, int tx) {
+                                          float* dSs, int row0, int col0, int kv_len, int shift, int64_t mask_base,
+                                          int ty, int tx) {
   constexpr int LP = TN + 1;
   const float c = a.scale * kLog2e;
   float s[4][4], dp[4][4];
@@ -105,8 +108,11 @@ __device__ __forceinline__ void tile_p_ds(const BwdArgs& a, const float* Qs, con
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int cidx = tx + 16 * j, col = col0 + cidx;
-      const bool keep = row < a.Lq && col < kv_len && (!a.causal || col <= row);
-      const float p = keep ? exp2f(fmaf(s[i][j], c, -lse2)) : 0.f;
+      // a row without any participating key has LSE = -inf and P = 0
+      const bool keep = row < a.Lq && col < kv_len && (!a.causal || col <= row + shift) && lse_s[r] != -INFINITY;
+      float x = fmaf(s[i][j], c, -lse2);
+      if (a.mask.ptr && keep) x += mask_bias2<T>(a.mask, mask_base + row * a.mask.sl + col);
+      const float p = keep ? exp2f(x) : 0.f;
       if (Ps) Ps[r * LP + cidx] = p;
       dSs[r * LP + cidx] = p * (dp[i][j] - dl) * a.scale;
     }
@@ -147,7 +153,9 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(const BwdArgs a) {
     for (int j = 0; j < DC; ++j) dk[i][j] = 0.f, dv[i][j] = 0.f;
 
   const int n_q_tiles = (a.Lq + TM - 1) / TM;
-  const int qt_begin = a.causal ? col0 / TM : 0;
+  const int shift = causal_shift(a.causal, kv_len, a.Lq);
+  // first query tile with a row i such that col0 <= i + shift
+  const int qt_begin = a.causal ? (col0 - shift > 0 ? (col0 - shift) / TM : 0) : 0;
   if (col0 < kv_len) {
     for (int g = 0; g < group; ++g) {
       const int h = hk * group + g;
@@ -166,7 +174,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(const BwdArgs a) {
           delta_s[tid] = in ? delta[row0 + tid] : 0.f;
         }
         __syncthreads();
-        tile_p_ds<D>(a, Qs, Ks, Vs, dOs, lse_s, delta_s, Ps, dSs, row0, col0, kv_len, ty, tx);
+        tile_p_ds<T, D>(a, Qs, Ks, Vs, dOs, lse_s, delta_s, Ps, dSs, row0, col0, kv_len, shift,
+                        b * a.mask.sb + h * a.mask.sh, ty, tx);
         __syncthreads();
         // dV[kv][d] += sum_row P[row][kv] dO[row][d];  dK[kv][d] += sum_row dS[row][kv] Q[row][d]
 #pragma unroll 2
@@ -222,8 +231,9 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdArgs a) {
     int l = a.kv_lens[b];
     kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
   }
+  const int shift = causal_shift(a.causal, kv_len, a.Lq);
   int kv_end = kv_len;
-  if (a.causal && row0 + TM < kv_end) kv_end = row0 + TM;
+  if (a.causal && row0 + TM + shift < kv_end) kv_end = row0 + TM + shift > 0 ? row0 + TM + shift : 0;
   const int n_tiles = (kv_end + TN - 1) / TN;
 
   const T* q = reinterpret_cast<const T*>(a.q) + b * a.qs.b + h * a.qs.h;
@@ -250,7 +260,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdArgs a) {
     load_tile<T, D>(Ks, k, a.ks.s, col0, a.Skv, tid);
     load_tile<T, D>(Vs, v, a.vs.s, col0, a.Skv, tid);
     __syncthreads();
-    tile_p_ds<D>(a, Qs, Ks, Vs, dOs, lse_s, delta_s, nullptr, dSs, row0, col0, kv_len, ty, tx);
+    tile_p_ds<T, D>(a, Qs, Ks, Vs, dOs, lse_s, delta_s, nullptr, dSs, row0, col0, kv_len, shift,
+                    b * a.mask.sb + h * a.mask.sh, ty, tx);
     __syncthreads();
 #pragma unroll 4
     for (int cc = 0; cc < TN; ++cc) {

@@ -94,7 +94,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-template <int D, bool BF16>
+// GEN: the general variant (a mask and / or a causal triangle that is not top-left
+// aligned); the fast variant compiles all of that out.
+template <int D, bool BF16, bool GEN>
 __global__ void __launch_bounds__(kThreads, 1)
     bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -126,7 +128,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
   }
   const int n_q_tiles = (a.Lq + BQ - 1) / BQ;
-  const int qt_begin = a.causal ? nt : 0;  // BM == BQ: query tiles before the key tile see none of it
+  const int shift = GEN ? causal_shift(a.causal, kv_len, a.Lq) : 0;  // key j participates iff j <= i + shift
+  // BM == BQ: query tiles before the key tile see none of it (general: first tile with a row i >= kv0 - shift)
+  const int qt_begin = a.causal ? (GEN ? (kv0 - shift > 0 ? (kv0 - shift) / BQ : 0) : nt) : 0;
   const int per_head = (kv0 < kv_len && qt_begin < n_q_tiles) ? n_q_tiles - qt_begin : 0;
   const int n_steps = per_head * group;
 
@@ -289,7 +293,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       dl = 0.f;
       if (q < a.Lq) {
         const int64_t idx = (static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q;
-        lse2 = -a.lse[idx] * kLog2e;
+        const float lse = a.lse[idx];
+        lse2 = lse == -INFINITY ? -INFINITY : -lse * kLog2e;  // a row without any participating key: P = 0
         dl = -a.delta[idx] * a.scale;
       }
     };
@@ -360,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
       TT_BSTAMP(wg, 2);
       ptx::tc_fence_after();
-      const bool diag = a.causal && q0 < kv0 + BM;  // some (query, key) pairs of this step are masked
+      const bool diag = a.causal && q0 + shift < kv0 + BM;  // some (query, key) pairs of this step are masked
       const bool masked = diag || kv0 + BM > kv_len;
 #pragma unroll
       for (int sc = 0; sc < 2; ++sc) {
@@ -379,9 +384,20 @@ __global__ void __launch_bounds__(kThreads, 1)
                                 make_float2(l4.x, l4.y));
           float2 x1 = ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v,
                                 make_float2(l4.z, l4.w));
+          if constexpr (GEN) {
+            if (a.mask.ptr && kv_row < a.Skv) {
+              // the mask element of (query, this thread's key): adjacent threads read adjacent keys
+              const int q = q0 + col + i;
+              const int64_t mo = b * a.mask.sb + (hk * group + n / per_head) * a.mask.sh + q * a.mask.sl + kv_row;
+              if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, mo);
+              if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, mo + a.mask.sl);
+              if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, mo + 2 * a.mask.sl);
+              if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, mo + 3 * a.mask.sl);
+            }
+          }
           float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), ptx::ex2(x1.y));
           if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
-            const int q = q0 + col + i;
+            const int q = q0 + col + i + shift;
             if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
             if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
             if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
@@ -502,7 +518,7 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const BwdArgs a) {
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool GEN>
 cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t stream) {
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   CUtensorMap tq, tk, tv, tdo, tdq;
@@ -514,7 +530,7 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   const size_t acc_bytes = static_cast<size_t>(a.B) * a.Hq * a.Lq * D * sizeof(float);
   cudaError_t e = cudaMemsetAsync(a.dq_accum, 0, acc_bytes, stream);
   if (e != cudaSuccess) return e;
-  auto kern = bwd_tc_kernel<D, BF16>;
+  auto kern = bwd_tc_kernel<D, BF16, GEN>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
   if (e != cudaSuccess) return e;
   dim3 grid((a.Skv + BM - 1) / BM, a.Hkv, a.B);
@@ -529,13 +545,21 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
 
 }  // namespace
 
+template <bool GEN>
+cudaError_t launch_g(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream) {
+  const bool bf = dtype == TT_ATTN_BF16;
+  if (D == 128)
+    return bf ? launch_t<128, true, GEN>(a, dtype, device, stream) : launch_t<128, false, GEN>(a, dtype, device, stream);
+  if (D == 64)
+    return bf ? launch_t<64, true, GEN>(a, dtype, device, stream) : launch_t<64, false, GEN>(a, dtype, device, stream);
+  return cudaErrorInvalidValue;
+}
+
 cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream) {
   cudaError_t e = launch_bwd_delta(dtype, D, a, stream);
   if (e != cudaSuccess) return e;
-  const bool bf = dtype == TT_ATTN_BF16;
-  if (D == 128) return bf ? launch_t<128, true>(a, dtype, device, stream) : launch_t<128, false>(a, dtype, device, stream);
-  if (D == 64) return bf ? launch_t<64, true>(a, dtype, device, stream) : launch_t<64, false>(a, dtype, device, stream);
-  return cudaErrorInvalidValue;
+  const bool general = a.mask.ptr != nullptr || a.causal == TT_ATTN_CAUSAL_BOTTOM_RIGHT;
+  return general ? launch_g<true>(dtype, D, a, device, stream) : launch_g<false>(dtype, D, a, device, stream);
 }
 
 }  // namespace ttattn

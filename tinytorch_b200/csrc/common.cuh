@@ -24,6 +24,13 @@ inline Str3 dense_or(const tt_attn_strides& st, int64_t H, int64_t S, int64_t D)
   return Str3{st.b, st.h, st.s};
 }
 
+// Optional mask, broadcast against [B, Hq, Lq, Skv]; the key dimension is contiguous.
+struct MaskArgs {
+  const void* ptr;  // null: no mask
+  int kind;         // tt_attn_mask_kind
+  int64_t sb, sh, sl;
+};
+
 // Arguments common to the prefill kernels (SIMT and tensor-core).
 struct FwdArgs {
   const void* q;
@@ -33,10 +40,11 @@ struct FwdArgs {
   float* lse;
   Str3 qs, ks, vs, os;
   int B, Hq, Hkv, Lq, Skv;
-  int causal;
+  int causal;  // tt_attn_causal
   float scale;
   const int32_t* kv_lens;
   int32_t* status;
+  MaskArgs mask;
   int* sched;  // tensor-core path: work counter in scratch memory, zeroed by the launcher
 };
 
@@ -54,10 +62,11 @@ struct BwdArgs {
   void* dv;
   Str3 qs, ks, vs, os, dos, dqs, dks, dvs;
   int B, Hq, Hkv, Lq, Skv;
-  int causal;
+  int causal;  // tt_attn_causal
   float scale;
   const int32_t* kv_lens;
   int32_t* status;
+  MaskArgs mask;
 };
 
 struct DecodeArgs {
@@ -117,6 +126,21 @@ __device__ __forceinline__ __half from_f32<__half>(float x) {
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
   return __float2bfloat16_rn(x);
+}
+
+
+// Query i sees key j under a causal mask iff j <= i + causal_shift(...).
+__host__ __device__ __forceinline__ int causal_shift(int causal, int kv_len, int Lq) {
+  return causal == TT_ATTN_CAUSAL_BOTTOM_RIGHT ? kv_len - Lq : 0;
+}
+
+// What the mask adds to the scaled score of one (query, key) pair, in log2
+// units: 0 or -inf for a boolean mask.  `off` is the element offset of the pair.
+template <typename T>
+__device__ __forceinline__ float mask_bias2(const MaskArgs& m, int64_t off) {
+  if (m.kind == TT_ATTN_MASK_BOOL) return reinterpret_cast<const uint8_t*>(m.ptr)[off] ? 0.f : -INFINITY;
+  if (m.kind == TT_ATTN_MASK_ADD_F32) return reinterpret_cast<const float*>(m.ptr)[off] * kLog2e;
+  return to_f32<T>(reinterpret_cast<const T*>(m.ptr)[off]) * kLog2e;
 }
 
 }  // namespace ttattn

@@ -56,10 +56,12 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const FwdArgs a) {
     int l = a.kv_lens[b];
     kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
   }
+  const int shift = causal_shift(a.causal, kv_len, a.Lq);
   int kv_end = kv_len;
-  if (a.causal && row0 + TM < kv_end) kv_end = row0 + TM;
+  if (a.causal && row0 + TM + shift < kv_end) kv_end = row0 + TM + shift > 0 ? row0 + TM + shift : 0;
   const int n_tiles = (kv_end + TN - 1) / TN;
   const float c = a.scale * kLog2e;
+  const int64_t mask_base = b * a.mask.sb + h * a.mask.sh;
 
   load_tile<T, D>(Qs, q, a.qs.s, row0, a.Lq, tid);
 
@@ -102,22 +104,25 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const FwdArgs a) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int col = col0 + tx + 16 * j;
-        const bool keep = col < kv_len && (!a.causal || col <= row);
+        const bool keep = col < kv_len && (!a.causal || col <= row + shift);
         s[i][j] = keep ? s[i][j] * c : -INFINITY;
+        if (a.mask.ptr && keep && row < a.Lq) s[i][j] += mask_bias2<T>(a.mask, mask_base + row * a.mask.sl + col);
         mx = fmaxf(mx, s[i][j]);
       }
 #pragma unroll
       for (int o = 8; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_new = fmaxf(m[i], mx);
-      // m_new is finite: every tile holds at least one kept key for each row
-      const float alpha = exp2f(m[i] - m_new);
+      // a row that has seen no participating key yet keeps m = -inf; its
+      // exponentials are taken against 0 and are all 0
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m[i] - m_use);
       m[i] = m_new;
       l[i] *= alpha;
 #pragma unroll
       for (int j = 0; j < DC; ++j) acc[i][j] *= alpha;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float p = exp2f(s[i][j] - m_new);
+        const float p = exp2f(s[i][j] - m_use);
         l[i] += p;
         Ps[(ty + 16 * i) * LP + tx + 16 * j] = p;
       }

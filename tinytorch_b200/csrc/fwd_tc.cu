@@ -104,9 +104,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // One work item, decoded identically by every role.
 struct Item {
-  int b, h, hk, row0, kv_len, nt0, nt1, n_max;
+  int b, h, hk, row0, kv_len, nt0, nt1, n_max, shift;
 };
 
+// GEN: the general variant of the kernel (a mask and / or a causal triangle that is
+// not top-left aligned); the fast variant compiles all of that out.
+template <bool GEN>
 __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs) {
   Item it;
   const int bh = w / n_pairs;
@@ -123,9 +126,12 @@ __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs
   it.kv_len = kv_len;
   // Number of key tiles each query tile walks (0 for a tile wholly beyond Lq).
   int e0 = kv_len, e1 = kv_len;
+  it.shift = GEN ? causal_shift(a.causal, kv_len, a.Lq) : 0;  // key j participates iff j <= i + shift
   if (a.causal) {
-    if (it.row0 + BM < e0) e0 = it.row0 + BM;
-    if (it.row0 + 2 * BM < e1) e1 = it.row0 + 2 * BM;
+    int c0 = it.row0 + BM + it.shift, c1 = it.row0 + 2 * BM + it.shift;
+    if (GEN) c0 = c0 > 0 ? c0 : 0, c1 = c1 > 0 ? c1 : 0;
+    if (c0 < e0) e0 = c0;
+    if (c1 < e1) e1 = c1;
   }
   it.nt0 = (it.row0 < a.Lq) ? (e0 + BN - 1) / BN : 0;
   it.nt1 = (it.row0 + BM < a.Lq) ? (e1 + BN - 1) / BN : 0;
@@ -133,7 +139,50 @@ __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs
   return it;
 }
 
-template <int D, bool BF16>
+// s[e] <- c * s[e] + mask(row, col0 + e) * log2(e) for the 128 scores of one
+// query row; `off` is the mask's element offset of (row, col0) and n_valid the
+// number of keys that exist from col0 on.  16-byte loads when the row segment is
+// whole and aligned, element loads otherwise.
+template <typename T>
+__device__ __forceinline__ void add_mask_row(uint32_t (&s)[BN], const MaskArgs& m, int64_t off, int n_valid, float c) {
+  const int esz = m.kind == TT_ATTN_MASK_BOOL ? 1 : (m.kind == TT_ATTN_MASK_ADD_F32 ? 4 : 2);
+  const uint8_t* base = reinterpret_cast<const uint8_t*>(m.ptr) + off * esz;
+  const bool fast = n_valid >= BN && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+#pragma unroll
+  for (int ch = 0; ch < BN / 16; ++ch) {
+    float bias[16];
+    if (fast) {
+      if (m.kind == TT_ATTN_MASK_BOOL) {
+        const uint4 v = *reinterpret_cast<const uint4*>(base + ch * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) bias[i] = ((w[i >> 2] >> ((i & 3) * 8)) & 0xffu) ? 0.f : -INFINITY;
+      } else if (m.kind == TT_ATTN_MASK_ADD_F32) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 v = *reinterpret_cast<const float4*>(base + ch * 64 + q * 16);
+          bias[q * 4 + 0] = v.x * kLog2e, bias[q * 4 + 1] = v.y * kLog2e;
+          bias[q * 4 + 2] = v.z * kLog2e, bias[q * 4 + 3] = v.w * kLog2e;
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint4 v = *reinterpret_cast<const uint4*>(base + ch * 32 + q * 16);
+          const T* t = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) bias[q * 8 + i] = to_f32<T>(t[i]) * kLog2e;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) bias[i] = (ch * 16 + i < n_valid) ? mask_bias2<T>(m, off + ch * 16 + i) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s[ch * 16 + i] = __float_as_uint(fmaf(__uint_as_float(s[ch * 16 + i]), c, bias[i]));
+  }
+}
+
+template <int D, bool BF16, bool GEN>
 __global__ void __launch_bounds__(kThreads, 1)
     fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -212,7 +261,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ctl->item[slot] = w;
           ptx::mbar_arrive(&ctl->item_full[slot]);
           if (w < 0) break;
-          const Item it = decode_item(a, w, n_pairs);
+          const Item it = decode_item<GEN>(a, w, n_pairs);
           if (it.n_max == 0) continue;
           if (!ptx::mbar_wait(&ctl->q_empty, (qc & 1) ^ 1, abort_flag)) break;
           ptx::mbar_arrive_expect_tx(&ctl->q_full, QT * TB);
@@ -295,7 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int w = ctl->item[slot];
           ptx::mbar_arrive(&ctl->item_empty[slot]);
           if (w < 0) break;
-          const Item it = decode_item(a, w, n_pairs);
+          const Item it = decode_item<GEN>(a, w, n_pairs);
           if (it.n_max == 0) continue;
           const int nt0 = it.nt0, nt1 = it.nt1, n_max = it.n_max;
           auto nt = [&](int t) { return t == 0 ? nt0 : nt1; };
@@ -352,8 +401,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + t * 128 + lane_addr;
     const uint32_t tO = tmem + 256 + t * D + lane_addr;
-    const float c = fabsf(a.scale) * kLog2e;
-    const float2 c2 = make_float2(c, c);
+    // > 0 so that a masked (-inf) score stays -inf when it is scaled
+    const float c = fmaxf(fabsf(a.scale) * kLog2e, 1e-30f);
+    // with a mask the scores are scaled when the mask is added, and the rest of the loop multiplies by 1
+    const float cm = (GEN && a.mask.ptr) ? 1.f : c;
+    const float2 c2 = make_float2(cm, cm);
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     uint32_t cnt = 0;  // softmax iterations completed (s_full phase)
     uint32_t ec = 0;   // items with work completed (o_full phase)
@@ -374,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int w = ctl->item[slot];
       ptx::mbar_arrive(&ctl->item_empty[slot]);
       if (w < 0) break;
-      const Item it = decode_item(a, w, n_pairs);
+      const Item it = decode_item<GEN>(a, w, n_pairs);
       const int n_t = t == 0 ? it.nt0 : it.nt1;
       TT_STAMP(1);
 #ifdef TT_ATTN_PROFILE
@@ -410,11 +462,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         TT_FINE(1);
 
         const int col0 = j * BN;
-        const bool mask_tile = (col0 + BN > kv_len) || (a.causal && col0 + BN - 1 > tile_row0);
+        if constexpr (GEN) {
+          if (a.mask.ptr && row < a.Lq)
+            add_mask_row<T>(s, a.mask, it.b * a.mask.sb + it.h * a.mask.sh + row * a.mask.sl + col0, a.Skv - col0, c);
+        }
+        const bool mask_tile = (col0 + BN > kv_len) || (a.causal && col0 + BN - 1 > tile_row0 + it.shift);
         if (mask_tile) {
           // Highest valid column of this row within the tile.
           int lim = kv_len - 1 - col0;
-          if (a.causal && row - col0 < lim) lim = row - col0;
+          if (a.causal && row + it.shift - col0 < lim) lim = row + it.shift - col0;
 #pragma unroll
           for (int e = 0; e < BN; ++e)
             if (e > lim) s[e] = 0xff800000u;  // -inf
@@ -439,11 +495,14 @@ __global__ void __launch_bounds__(kThreads, 1)
               for (int q = 0; q < 8; ++q)
                 mx[q] = ptx::max3(mx[q], __uint_as_float(s[e + q]), __uint_as_float(s[e + q + 8]));
             const float x_max =
-                ptx::max3(ptx::max3(mx[0], mx[1], mx[2]), ptx::max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
+                ptx::max3(ptx::max3(mx[0], mx[1], mx[2]), ptx::max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * cm;
             if (j == 0) {
               m_ref = x_max;
-            } else if (x_max > m_ref) {
-              const float alpha = ptx::ex2(m_ref - x_max);
+            } else if (__any_sync(0xffffffffu, x_max > m_ref)) {
+              // tcgen05.ld / .st are warp-collective: every lane takes part, lanes
+              // whose maximum did not grow with alpha = 1
+              const float m_new = fmaxf(m_ref, x_max);
+              const float alpha = (GEN && m_new == -INFINITY) ? 1.f : ptx::ex2(m_ref - m_new);
               uint32_t r[32];
 #pragma unroll
               for (int cc = 0; cc < D / 32; ++cc) {
@@ -454,12 +513,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                 ptx::tmem_st32(tO + cc * 32, r);
               }
               l2.x *= alpha, l2.y *= alpha;
-              m_ref = x_max;
+              m_ref = m_new;
             }
           }
           // P = 2^(c*s - m_ref) in packed fp32 pairs; two halves of 64 columns so that
           // the packed 16-bit P of the first half is stored while the second is computed.
-          const float2 nm2 = make_float2(-m_ref, -m_ref);
+          // (general variant) a row that has seen no participating key yet keeps
+          // m_ref = -inf; its exponentials are taken against 0 and are all 0
+          const float m_use = (GEN && m_ref == -INFINITY) ? 0.f : m_ref;
+          const float2 nm2 = make_float2(-m_use, -m_use);
           float2 lt = make_float2(0.f, 0.f);
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -477,7 +539,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float tile_sum = lt.x + lt.y;
           // redo with a fresh maximum if any row of the warp needs it (tcgen05.ld /
           // .st are warp-collective, so the warp decides together)
-          const bool redo = !need_max && !(tile_sum <= 256.f);
+          // ... and such a row takes the maximum of every tile until it has one
+          const bool redo = !need_max && (!(tile_sum <= 256.f) || (GEN && m_ref == -INFINITY));
           if (!__any_sync(0xffffffffu, redo)) {
             l2 = ptx::add2(l2, lt);
             break;
@@ -547,13 +610,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ------------------------------------------------------------------ host ----
-template <int D, bool BF16>
+template <int D, bool BF16, bool GEN>
 cudaError_t launch_t(const FwdArgs& a, int dtype, int device, cudaStream_t stream) {
   CUtensorMap tq, tk, tv, to;
   if (!make_map(&tq, dtype, a.q, D, a.Lq, a.Hq, a.B, a.qs) || !make_map(&tk, dtype, a.k, D, a.Skv, a.Hkv, a.B, a.ks) ||
       !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs) || !make_map(&to, dtype, a.o, D, a.Lq, a.Hq, a.B, a.os))
     return cudaErrorInvalidValue;
-  auto kern = fwd_tc_kernel<D, BF16>;
+  auto kern = fwd_tc_kernel<D, BF16, GEN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
   if (e != cudaSuccess) return e;
   // the work counter must start at zero for every launch
@@ -568,11 +631,20 @@ cudaError_t launch_t(const FwdArgs& a, int dtype, int device, cudaStream_t strea
 
 }  // namespace
 
-cudaError_t launch_fwd_tc(int dtype, int D, const FwdArgs& a, int device, cudaStream_t stream) {
+template <bool GEN>
+cudaError_t launch_g(int dtype, int D, const FwdArgs& a, int device, cudaStream_t stream) {
   const bool bf = dtype == TT_ATTN_BF16;
-  if (D == 128) return bf ? launch_t<128, true>(a, dtype, device, stream) : launch_t<128, false>(a, dtype, device, stream);
-  if (D == 64) return bf ? launch_t<64, true>(a, dtype, device, stream) : launch_t<64, false>(a, dtype, device, stream);
+  if (D == 128)
+    return bf ? launch_t<128, true, GEN>(a, dtype, device, stream) : launch_t<128, false, GEN>(a, dtype, device, stream);
+  if (D == 64)
+    return bf ? launch_t<64, true, GEN>(a, dtype, device, stream) : launch_t<64, false, GEN>(a, dtype, device, stream);
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_fwd_tc(int dtype, int D, const FwdArgs& a, int device, cudaStream_t stream) {
+  // the general variant only where it is needed: the fast one carries none of its code
+  const bool general = a.mask.ptr != nullptr || a.causal == TT_ATTN_CAUSAL_BOTTOM_RIGHT;
+  return general ? launch_g<true>(dtype, D, a, device, stream) : launch_g<false>(dtype, D, a, device, stream);
 }
 
 }  // namespace ttattn

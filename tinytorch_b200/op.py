@@ -53,12 +53,57 @@ def _common(p, ref):
     p.status = None
 
 
+def _causal_mode(isCausal):
+    """False/True as in the reference (top-left aligned triangle), or the string
+    "bottom-right" for a chunk of new queries at the end of the key sequence."""
+    if isCausal == "bottom-right":
+        return _capi.CAUSAL_BOTTOM_RIGHT
+    if isCausal in ("top-left", True, 1):
+        return _capi.CAUSAL_TOP_LEFT
+    if isCausal in (False, None, 0):
+        return _capi.CAUSAL_NONE
+    raise ValueError("isCausal must be a bool or 'top-left' / 'bottom-right'")
+
+
+def _set_mask(p, mask, q, L, S):
+    """attnMask of the reference (src/Function/FuncNNLayer.h:249-256): Bool -> keys that
+    participate, otherwise added to the scaled scores; any shape that broadcasts against
+    [B, Hq, L, S] by trailing-dimension alignment.  Returns the tensor to keep alive."""
+    if mask is None:
+        return None
+    if not mask.is_cuda or mask.device != q.device:
+        raise ValueError("attnMask must be on the device of q")
+    if mask.dim() > 4:
+        raise ValueError("attnMask has more than 4 dimensions")
+    m = mask.reshape((1,) * (4 - mask.dim()) + tuple(mask.shape))
+    B, Hq = q.shape[0], q.shape[1]
+    for have, want in zip(m.shape, (B, Hq, L, S)):
+        if have != want and have != 1:
+            raise ValueError("attnMask shape %s does not broadcast against %s" % (tuple(mask.shape), (B, Hq, L, S)))
+    if m.dtype == torch.bool:
+        m = m.view(torch.uint8)
+        kind = _capi.MASK_BOOL
+    elif m.dtype == q.dtype and q.dtype != torch.float32:
+        kind = _capi.MASK_ADD
+    else:
+        m = m.to(torch.float32)
+        kind = _capi.MASK_ADD_F32
+    if m.shape[3] != S or m.stride(3) != 1:
+        # keys must be contiguous in memory; a mask broadcast over keys is expanded
+        m = m.expand(m.shape[0], m.shape[1], m.shape[2], S).contiguous()
+    p.mask = m.data_ptr()
+    p.mask_kind = kind
+    for i in range(3):
+        p.mask_strides[i] = 0 if m.shape[i] == 1 else m.stride(i)
+    return m
+
+
 def default_scale(D):
     """1/sqrt(D) in fp32, the reference default (src/Function/FuncNNLayer.h:235)."""
     return 1.0 / math.sqrt(float(D))
 
 
-def sdpAttentionFwd(q, k, v, isCausal=False, scale=None, kvLens=None, needLse=True, status=None):
+def sdpAttentionFwd(q, k, v, isCausal=False, scale=None, kvLens=None, needLse=True, status=None, attnMask=None):
     """softmax(scale * Q K^T + bias) V  ->  (O [B,Hq,L,D], LSE [B,Hq,L] fp32 or None)."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_tensor(t, n)
@@ -75,9 +120,10 @@ def sdpAttentionFwd(q, k, v, isCausal=False, scale=None, kvLens=None, needLse=Tr
     p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
     p.lse = lse.data_ptr() if lse is not None else None
     p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides(q), _strides(k), _strides(v), _strides(o)
-    p.is_causal = 1 if isCausal else 0
+    p.is_causal = _causal_mode(isCausal)
     p.scale = default_scale(D) if scale is None else float(scale)
     p.kv_lens = kvLens.data_ptr() if kvLens is not None else None
+    keep = _set_mask(p, attnMask, q, L, S)  # noqa: F841 (alive until the launch is enqueued)
     _common(p, q)
     if status is not None:
         p.status = status.data_ptr()
@@ -85,7 +131,8 @@ def sdpAttentionFwd(q, k, v, isCausal=False, scale=None, kvLens=None, needLse=Tr
     return o, lse
 
 
-def sdpAttentionBwd(dO, q, k, v, o, lse, isCausal=False, scale=None, kvLens=None, needs=(True, True, True)):
+def sdpAttentionBwd(dO, q, k, v, o, lse, isCausal=False, scale=None, kvLens=None, needs=(True, True, True),
+                    attnMask=None):
     """Gradients (dQ, dK, dV); entries of `needs` that are False come back as None."""
     for t, n in ((dO, "dO"), (q, "q"), (k, "k"), (v, "v"), (o, "o")):
         _check_tensor(t, n)
@@ -111,9 +158,10 @@ def sdpAttentionBwd(dO, q, k, v, o, lse, isCausal=False, scale=None, kvLens=None
         p.dk_strides = _strides(dk)
     if dv is not None:
         p.dv_strides = _strides(dv)
-    p.is_causal = 1 if isCausal else 0
+    p.is_causal = _causal_mode(isCausal)
     p.scale = default_scale(D) if scale is None else float(scale)
     p.kv_lens = kvLens.data_ptr() if kvLens is not None else None
+    keep = _set_mask(p, attnMask, q, L, S)  # noqa: F841
     _common(p, q)
     _capi.check(_capi.lib().tt_attn_bwd(C.byref(p)))
     return dq, dk, dv

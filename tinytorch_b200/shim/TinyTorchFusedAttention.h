@@ -14,7 +14,8 @@
  *   - function::sdpAttentionFused(query, key, value, isCausal, attnMask, dropoutP, scale),
  *     signature-identical to function::sdpAttention (src/Function/FuncNNLayer.h:298-302).
  *     Calls the fused path when it applies (CUDA tensors, D in {64,128}, no
- *     dropout, mask absent) and otherwise forwards to the original composition.
+ *     dropout, a mask that is absent or of a supported form) and otherwise forwards to the
+ *     original composition.
  * Error convention: a non-zero status is logged with LOGE and then ASSERT(false)
  * fires, which is what every reference op does on failure (src/Utils/Macros.h:34-43).
  */
@@ -54,8 +55,37 @@ inline tt_attn_strides denseStrides(const Tensor& t) {
   return tt_attn_strides{t.stride(0), t.stride(1), t.stride(2)};
 }
 
+// attnMask (src/Function/FuncNNLayer.h:249-256) runs fused when it is Bool, Float32 or the
+// tensors' dtype, has at most 4 dimensions, spans all keys in its last dimension and
+// broadcasts against [B, H, L, S] in the others.
+inline bool maskApplicable(const Tensor& mask, const Tensor& q, const Tensor& k) {
+  if (!mask.defined()) return true;
+  if (mask.dim() < 1 || mask.dim() > 4 || mask.size(-1) != k.size(2)) return false;
+  if (mask.dtype() != DType::Bool && mask.dtype() != DType::Float32 && mask.dtype() != q.dtype()) return false;
+  const int64_t want[3] = {q.size(0), q.size(1), q.size(2)};
+  for (int64_t i = 0; i < mask.dim() - 1; i++) {
+    const int64_t have = mask.size(i), full = want[3 - (mask.dim() - 1) + i];
+    if (have != 1 && have != full) return false;
+  }
+  return true;
+}
+
+// Fills the mask fields of a parameter struct (fwd and bwd share their names).
+template <typename P>
+inline void setMask(P& p, const Tensor& mask, const Tensor& /*q*/) {
+  if (!mask.defined()) return;
+  p.mask = mask.dataPtr<>();
+  p.mask_kind = mask.dtype() == DType::Bool      ? TT_ATTN_MASK_BOOL
+                : mask.dtype() == DType::Float32 ? TT_ATTN_MASK_ADD_F32
+                                                 : TT_ATTN_MASK_ADD;  // the tensors' 16-bit dtype
+  // trailing-dimension alignment (src/Tensor/TensorIterator.cpp:73-106); extent 1 broadcasts
+  for (int64_t i = 0; i < mask.dim() - 1; i++)
+    p.mask_strides[3 - (mask.dim() - 1) + i] = mask.size(i) == 1 ? 0 : mask.stride(i);
+}
+
 inline bool applicable(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float dropoutP) {
-  if (!q.device().isCuda() || mask.defined() || dropoutP > 0.f) return false;
+  if (!q.device().isCuda() || dropoutP > 0.f) return false;
+  if (q.dim() == 4 && k.dim() == 4 && !maskApplicable(mask, q, k)) return false;
   if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4) return false;
   if (q.dtype() != k.dtype() || q.dtype() != v.dtype()) return false;
   if (q.dtype() != DType::Float32 && q.dtype() != DType::Float16 && q.dtype() != DType::BFloat16) return false;
@@ -68,10 +98,10 @@ inline bool applicable(const Tensor& q, const Tensor& k, const Tensor& v, const 
 namespace op {
 
 using SDPAttentionFwdOpFn = TensorPair (*)(const Tensor& q, const Tensor& k, const Tensor& v, bool isCausal,
-                                           float scale, const Tensor& kvLens);
+                                           float scale, const Tensor& kvLens, const Tensor& mask);
 using SDPAttentionBwdOpFn = TensorList (*)(const Tensor& dO, const Tensor& q, const Tensor& k, const Tensor& v,
                                            const Tensor& o, const Tensor& lse, bool isCausal, float scale,
-                                           const Tensor& kvLens);
+                                           const Tensor& kvLens, const Tensor& mask);
 using SDPAttentionDecodeOpFn = Tensor (*)(const Tensor& q, const Tensor& kCache, const Tensor& vCache,
                                           const Tensor& kvLens, float scale);
 
@@ -80,7 +110,7 @@ DEFINE_OP(sdpAttentionBwd, SDPAttentionBwdOpFn)
 DEFINE_OP(sdpAttentionDecode, SDPAttentionDecodeOpFn)
 
 inline TensorPair sdpAttentionFwdCudaImpl(const Tensor& q, const Tensor& k, const Tensor& v, bool isCausal,
-                                          float scale, const Tensor& kvLens) {
+                                          float scale, const Tensor& kvLens, const Tensor& mask) {
   const int device = q.device().index;
   Tensor o(q.shape(), q.options().noGrad());
   Tensor lse({q.size(0), q.size(1), q.size(2)}, q.options().noGrad().dtype(DType::Float32));
@@ -97,6 +127,7 @@ inline TensorPair sdpAttentionFwdCudaImpl(const Tensor& q, const Tensor& k, cons
   p.is_causal = isCausal ? 1 : 0;
   p.scale = scale;
   p.kv_lens = kvLens.defined() ? kvLens.dataPtr<int32_t>() : nullptr;
+  fused_detail::setMask(p, mask, q);
   p.device = device;
   p.stream = cuda::getCurrentCUDAStream(device).stream();
   p.alloc = fused_detail::allocHook();
@@ -106,7 +137,7 @@ inline TensorPair sdpAttentionFwdCudaImpl(const Tensor& q, const Tensor& k, cons
 
 inline TensorList sdpAttentionBwdCudaImpl(const Tensor& dO, const Tensor& q, const Tensor& k, const Tensor& v,
                                           const Tensor& o, const Tensor& lse, bool isCausal, float scale,
-                                          const Tensor& kvLens) {
+                                          const Tensor& kvLens, const Tensor& mask) {
   const int device = q.device().index;
   Tensor dq(q.shape(), q.options().noGrad());
   Tensor dk(k.shape(), k.options().noGrad());
@@ -127,6 +158,7 @@ inline TensorList sdpAttentionBwdCudaImpl(const Tensor& dO, const Tensor& q, con
   p.is_causal = isCausal ? 1 : 0;
   p.scale = scale;
   p.kv_lens = kvLens.defined() ? kvLens.dataPtr<int32_t>() : nullptr;
+  fused_detail::setMask(p, mask, q);
   p.device = device;
   p.stream = cuda::getCurrentCUDAStream(device).stream();
   p.alloc = fused_detail::allocHook();
@@ -173,9 +205,9 @@ class FuncSDPAttentionFused : public Function<FuncSDPAttentionFused> {
  public:
   static Tensor forward(AutogradContext* ctx, const Tensor& query, const Tensor& key, const Tensor& value,
                         bool isCausal, const Tensor& attnMask, float dropoutP, std::optional<float> scale) {
-    ASSERT(!attnMask.defined() && dropoutP == 0.f);
+    ASSERT(!(isCausal && attnMask.defined()) && dropoutP == 0.f);  // as src/Function/FuncNNLayer.h:242
     const float s = scale.has_value() ? scale.value() : (1.f / std::sqrt(static_cast<float>(query.size(-1))));
-    auto [o, lse] = op::sdpAttentionFwd(query, key, value, isCausal, s, Tensor{});
+    auto [o, lse] = op::sdpAttentionFwd(query, key, value, isCausal, s, Tensor{}, attnMask);
     if (ctx) {
       // savedInputs holds every Tensor argument in order: query, key, value, attnMask
       ctx->pushData(o);
@@ -194,7 +226,8 @@ class FuncSDPAttentionFused : public Function<FuncSDPAttentionFused> {
     auto lse = ctx->popData().toTensor();
     const bool isCausal = ctx->popData().toBool();
     const float s = ctx->popData().toFloat();
-    auto grads = op::sdpAttentionBwd(grad, query, key, value, o, lse, isCausal, s, Tensor{});
+    const Tensor mask = ctx->savedInputs.size() > 3 ? ctx->savedInputs[3] : Tensor{};
+    auto grads = op::sdpAttentionBwd(grad, query, key, value, o, lse, isCausal, s, Tensor{}, mask);
     if (query.requiresGrad()) query.addGrad(std::move(grads[0]));
     if (key.requiresGrad()) key.addGrad(std::move(grads[1]));
     if (value.requiresGrad()) value.addGrad(std::move(grads[2]));
