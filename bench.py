@@ -38,6 +38,9 @@ WORKLOADS = {
     "decode": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
     # reduced copies of the two headline workloads, sized for an ncu capture (inputs still larger than L2)
     "prefill_ncu": dict(kind="fwd", dtype="bf16", B=2, Hq=32, Hkv=32, L=4096, S=4096, D=128, causal=True, std=1.0),
+    # the fused decode step: rotary embedding + cache append + attention (same bytes, one more row per sequence)
+    "decode_append": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0,
+                          append=True),
     "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
@@ -280,9 +283,17 @@ def run_ours(args, w, wname):
         res = {}
         if wl["kind"] == "decode":
             lens_np = np.random.default_rng(1234 + rank).integers(1024, wl["S"] + 1, size=wl["B"]).astype(np.int32)
+            if wl.get("append"):
+                lens_np = np.minimum(lens_np, wl["S"] - 1)  # room for the step's row
             lens = torch.from_numpy(lens_np).to(dev)
-            fn = lambda: op.sdpAttentionDecode(q, k, v, lens)
-            work = decode_bytes(wl, lens_np)
+            if wl.get("append"):
+                kn, vn = k[:, :, :1].contiguous(), v[:, :, :1].contiguous()
+                cos, sin = op.ropeTables(wl["S"], wl["D"], device=dev)
+                fn = lambda: op.sdpAttentionDecodeAppend(q, kn, vn, k, v, lens, cos, sin)
+                work = decode_bytes(wl, lens_np + 1)
+            else:
+                fn = lambda: op.sdpAttentionDecode(q, k, v, lens)
+                work = decode_bytes(wl, lens_np)
             launches = 2
         elif wl["kind"] == "fwdbwd":
             do = torch.randn_like(q)

@@ -204,11 +204,53 @@ typedef struct tt_attn_decode_params {
   int32_t* status;
 } tt_attn_decode_params;
 
+/* One decode step of a token loop, fused (no counterpart in the reference, which has
+ * neither a KV cache object nor rotary embeddings; its consumer keeps the cache as
+ * plain tensors and would run these as separate ops before sdpAttention):
+ *   1. rotary position embedding of q and of the step's new key at position
+ *      p_b = kv_lens[b] (skipped when rope_cos is NULL);
+ *   2. the rotated key and the new value are written to row p_b of the caches;
+ *   3. attention of the rotated q over rows [0, p_b] as tt_attn_decode does.
+ * rope_cos / rope_sin are fp32 tables [rope_positions, D/2]; pair i of a row at
+ * position p turns by the angle whose cosine and sine are table[p][i].  The pairs
+ * are elements (i, i + D/2), or (2i, 2i+1) when rope_interleaved is non-zero.
+ * new_lens (optional, may not alias kv_lens) receives kv_lens[b] + 1.  A sequence
+ * whose cache is full (kv_lens[b] >= capacity) appends nothing, attends over the
+ * whole cache and sets bit 4 of *status; a position beyond the tables skips the
+ * rotation and sets bit 8. */
+typedef struct tt_attn_decode_append_params {
+  uint32_t struct_size;
+  int32_t dtype;
+  int32_t B, Hq, Hkv, capacity, D;
+  const void* q;      /* [B, Hq, 1, D] */
+  const void* k_new;  /* [B, Hkv, 1, D] */
+  const void* v_new;  /* [B, Hkv, 1, D] */
+  void* k_cache;      /* [B, Hkv, capacity, D]; row kv_lens[b] is written */
+  void* v_cache;
+  void* o;            /* [B, Hq, 1, D] */
+  float* lse;         /* [B, Hq] or NULL */
+  tt_attn_strides q_strides, k_new_strides, v_new_strides, k_strides, v_strides, o_strides;
+  float scale;
+  const int32_t* kv_lens; /* device [B], required: valid rows before this step */
+  int32_t* new_lens;      /* device [B] or NULL */
+  const float* rope_cos;  /* device [rope_positions, D/2] or NULL */
+  const float* rope_sin;
+  int32_t rope_positions;
+  int32_t rope_interleaved;
+  int32_t device;
+  void* stream;
+  void* workspace; /* as tt_attn_decode: tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, ...) */
+  size_t workspace_bytes;
+  const tt_attn_alloc_hook* alloc;
+  int32_t* status;
+} tt_attn_decode_append_params;
+
 enum tt_attn_kind { TT_ATTN_KIND_FWD = 0, TT_ATTN_KIND_BWD = 1, TT_ATTN_KIND_DECODE = 2 };
 
 TT_ATTN_API int tt_attn_fwd(const tt_attn_fwd_params* p);
 TT_ATTN_API int tt_attn_bwd(const tt_attn_bwd_params* p);
 TT_ATTN_API int tt_attn_decode(const tt_attn_decode_params* p);
+TT_ATTN_API int tt_attn_decode_append(const tt_attn_decode_append_params* p);
 
 /* Decode for callers that cannot give this library any device memory: hosts
  * where an embedding runtime owns the whole device heap and offers neither an

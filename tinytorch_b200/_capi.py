@@ -77,7 +77,25 @@ class DecodeParams(C.Structure):
     ]
 
 
-EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_static", "tt_attn_workspace_bytes", "tt_attn_strerror",
+class DecodeAppendParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("capacity", C.c_int32), ("D", C.c_int32),
+        ("q", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("q_strides", Strides), ("k_new_strides", Strides), ("v_new_strides", Strides),
+        ("k_strides", Strides), ("v_strides", Strides), ("o_strides", Strides),
+        ("scale", C.c_float),
+        ("kv_lens", C.c_void_p), ("new_lens", C.c_void_p),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("rope_positions", C.c_int32), ("rope_interleaved", C.c_int32),
+        ("device", C.c_int32), ("stream", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("alloc", C.POINTER(AllocHook)), ("status", C.c_void_p),
+    ]
+
+
+EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_append", "tt_attn_decode_static", "tt_attn_workspace_bytes", "tt_attn_strerror",
            "tt_attn_last_cuda_error", "tt_attn_version")
 
 _lib = None
@@ -101,6 +119,8 @@ def lib():
         L.tt_attn_fwd.argtypes = [C.POINTER(FwdParams)]
         L.tt_attn_bwd.argtypes = [C.POINTER(BwdParams)]
         L.tt_attn_decode.argtypes = [C.POINTER(DecodeParams)]
+        L.tt_attn_decode_append.argtypes = [C.POINTER(DecodeAppendParams)]
+        L.tt_attn_decode_append.restype = C.c_int
         L.tt_attn_decode_static.argtypes = [C.POINTER(DecodeParams)]
         L.tt_attn_decode_static.restype = C.c_int
         for n in ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_version"):

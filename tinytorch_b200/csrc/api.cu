@@ -250,6 +250,49 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
 
+int tt_attn_decode_append(const tt_attn_decode_append_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_attn_decode_append_params)) return TT_ATTN_ERR_STRUCT;
+  if (int rc = check_common(p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D)) return rc;
+  if (!p->q || !p->k_new || !p->v_new || !p->k_cache || !p->v_cache || !p->o || !p->kv_lens) return TT_ATTN_ERR_NULL;
+  if ((p->rope_cos == nullptr) != (p->rope_sin == nullptr)) return TT_ATTN_ERR_NULL;
+  if (p->rope_cos && p->rope_positions <= 0) return TT_ATTN_ERR_SHAPE;
+  if (p->new_lens && p->new_lens == p->kv_lens) return TT_ATTN_ERR_SHAPE;
+  const size_t es = elem_size(p->dtype);
+  DecodeArgs a{};
+  a.q = p->q, a.k = p->k_cache, a.v = p->v_cache, a.o = p->o, a.lse = p->lse;
+  a.k_new = p->k_new, a.v_new = p->v_new;
+  a.qs = dense_or(p->q_strides, p->Hq, 1, p->D);
+  a.ks = dense_or(p->k_strides, p->Hkv, p->capacity, p->D);
+  a.vs = dense_or(p->v_strides, p->Hkv, p->capacity, p->D);
+  a.os = dense_or(p->o_strides, p->Hq, 1, p->D);
+  const Str3 kn = dense_or(p->k_new_strides, p->Hkv, 1, p->D), vn = dense_or(p->v_new_strides, p->Hkv, 1, p->D);
+  a.kn_b = kn.b, a.kn_h = kn.h, a.vn_b = vn.b, a.vn_h = vn.h;
+  const void* ptrs[] = {p->q, p->k_new, p->v_new, p->k_cache, p->v_cache, p->o};
+  for (const void* q : ptrs)
+    if (!aligned16(q)) return TT_ATTN_ERR_ALIGN;
+  const Str3* sts[] = {&a.qs, &a.ks, &a.vs, &a.os, &kn, &vn};
+  for (const Str3* s : sts)
+    if (!strides_ok(*s, es)) return TT_ATTN_ERR_ALIGN;
+  a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.capacity = p->capacity;
+  a.scale = p->scale;
+  a.kv_lens = p->kv_lens;
+  a.new_lens = p->new_lens;
+  a.rope_cos = p->rope_cos, a.rope_sin = p->rope_sin;
+  a.rope_positions = p->rope_positions, a.rope_interleaved = p->rope_interleaved;
+  a.status = p->status;
+  decode_plan(p->capacity, &a.nsplit, &a.chunk);
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  Workspace ws;
+  const size_t need =
+      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
+  if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
+  a.partial = static_cast<float*>(ws.ptr);
+  cudaError_t e = launch_decode_append(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
 int tt_attn_decode_static(const tt_attn_decode_params* p) {
   if (!p) return TT_ATTN_ERR_NULL;
   if (p->struct_size != sizeof(tt_attn_decode_params)) return TT_ATTN_ERR_STRUCT;

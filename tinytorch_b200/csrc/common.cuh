@@ -14,6 +14,8 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 // Status bits a kernel may OR into the caller's status word.
 constexpr int kStatusWaitExpired = 1;
+constexpr int kStatusCacheFull = 4;      // decode-append: no free row in the cache of some sequence
+constexpr int kStatusRopeRange = 8;      // decode-append: position beyond the rotary tables
 
 struct Str3 {
   int64_t b, h, s;
@@ -81,6 +83,16 @@ struct DecodeArgs {
   int nsplit, chunk;
   float scale;
   const int32_t* kv_lens;
+  // append variant only: the step's new key / value row per (b, kv head), rotary tables, outputs
+  const void* k_new;
+  const void* v_new;
+  int64_t kn_b, kn_h, vn_b, vn_h;  // element strides of k_new / v_new
+  const float* rope_cos;           // [rope_positions, D/2] or null: no rotation
+  const float* rope_sin;
+  int rope_positions;
+  int rope_interleaved;            // pairs (2i, 2i+1) instead of (i, i + D/2)
+  int32_t* new_lens;               // optional [B]: kv_lens[b] + 1
+  int32_t* status;
 };
 
 // Each returns a cudaError_t from the launch (no synchronisation).
@@ -92,6 +104,8 @@ cudaError_t launch_bwd_delta(int dtype, int D, const BwdArgs& a, cudaStream_t st
 // fp16 / bf16 backward on the tensor cores; needs a.delta and a.dq_accum
 cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream);
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
+// rotary embedding of q and the new key, append of the new key / value row, then the same scan
+cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
 
 cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, int device, cudaStream_t stream,
                                  bool* too_large);

@@ -63,9 +63,57 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return r;
 }
 
-// G = query heads handled per pass (all share this CTA's kv head).
-template <typename T, int D, int G>
-__global__ void __launch_bounds__(kThreads) decode_kernel(const DecodeArgs a) {
+template <typename T>
+__device__ __forceinline__ uint4 pack16(const float (&f)[Vec16<T>::N]) {
+  if constexpr (sizeof(T) == 4) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  } else {
+    uint32_t u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      T lo = from_f32<T>(f[2 * i]), hi = from_f32<T>(f[2 * i + 1]);
+      u[i] = static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&lo)) |
+             (static_cast<uint32_t>(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+    }
+    return make_uint4(u[0], u[1], u[2], u[3]);
+  }
+}
+
+// Rotary position embedding of one row at position `pos`, applied to the lane's
+// slice x[0..N) = elements [d0, d0+N) of the row.  Pairs are (i, i + D/2), the two
+// halves living LPK/2 lanes apart (every lane of the warp must call this), or
+// (2i, 2i+1) inside the slice when `interleaved`.  Pair i turns by the angle whose
+// cosine / sine are cos[pos][i] / sin[pos][i].
+template <int N, int LPK, int D>
+__device__ __forceinline__ void rope_slice(float (&x)[N], const float* cos, const float* sin, int pos, int d0,
+                                           bool interleaved) {
+  const float* cp = cos + static_cast<int64_t>(pos) * (D / 2);
+  const float* sp = sin + static_cast<int64_t>(pos) * (D / 2);
+  if (interleaved) {
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      const float c = cp[(d0 + i) >> 1], s = sp[(d0 + i) >> 1];
+      const float a = x[i], b = x[i + 1];
+      x[i] = a * c - b * s;
+      x[i + 1] = b * c + a * s;
+    }
+  } else {
+    const bool upper = d0 >= D / 2;
+    const int f0 = upper ? d0 - D / 2 : d0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], LPK / 2);
+      const float c = cp[f0 + i], s = sp[f0 + i];
+      x[i] = upper ? x[i] * c + other * s : x[i] * c - other * s;
+    }
+  }
+}
+
+// G = query heads handled per pass (all share this CTA's kv head).  APPEND: the
+// step's new key / value row is rotated, written to the cache at row kv_len[b] and
+// attended to like any other row; q is rotated to the same position.
+template <typename T, int D, int G, bool APPEND>
+__global__ void __launch_bounds__(kThreads, G == 1 ? 3 : 1) decode_kernel(const DecodeArgs a) {
   constexpr int N = Vec16<T>::N;  // elements per 16-byte slice
   constexpr int LPK = D / N;      // lanes per cache row
   constexpr int KPW = 32 / LPK;   // rows per warp-wide load
@@ -83,12 +131,42 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const DecodeArgs a) {
     int l = a.kv_lens[b];
     len = l < 0 ? 0 : (l < a.capacity ? l : a.capacity);
   }
+  const T* kbase = reinterpret_cast<const T*>(a.k) + b * a.ks.b + hk * a.ks.h + d0;
+  const T* vbase = reinterpret_cast<const T*>(a.v) + b * a.vs.b + hk * a.vs.h + d0;
+
+  int pos = 0;  // APPEND: position of the step's token
+  bool rotate = false;
+  if constexpr (APPEND) {
+    pos = len;
+    rotate = a.rope_cos != nullptr && pos < a.rope_positions;
+    if (tid == 0 && a.status && a.rope_cos != nullptr && !rotate) atomicOr(a.status, kStatusRopeRange);
+    if (pos < a.capacity) {
+      // the one CTA of this (b, kv head) whose chunk holds row `pos` writes it;
+      // no other CTA reads that row
+      if (split == pos / a.chunk) {
+        if (warp == 0) {
+          const T* kn = reinterpret_cast<const T*>(a.k_new) + b * a.kn_b + hk * a.kn_h + d0;
+          float kf[N];
+          Vec16<T>::unpack(*reinterpret_cast<const uint4*>(kn), kf);
+          if (rotate) rope_slice<N, LPK, D>(kf, a.rope_cos, a.rope_sin, pos, d0, a.rope_interleaved != 0);
+          if (sub == 0) {
+            const T* vn = reinterpret_cast<const T*>(a.v_new) + b * a.vn_b + hk * a.vn_h + d0;
+            *reinterpret_cast<uint4*>(const_cast<T*>(kbase) + static_cast<int64_t>(pos) * a.ks.s) = pack16<T>(kf);
+            *reinterpret_cast<uint4*>(const_cast<T*>(vbase) + static_cast<int64_t>(pos) * a.vs.s) =
+                *reinterpret_cast<const uint4*>(vn);
+          }
+        }
+        __syncthreads();  // the row is in the cache before this CTA scans it
+      }
+      len = pos + 1;
+    } else if (tid == 0 && a.status) {
+      atomicOr(a.status, kStatusCacheFull);  // nothing appended; the scan covers the full cache
+    }
+    if (split == 0 && hk == 0 && tid == 0 && a.new_lens) a.new_lens[b] = len;
+  }
   const int begin = split * a.chunk;
   const int end = min(len, begin + a.chunk);
   const float c = a.scale * kLog2e;
-
-  const T* kbase = reinterpret_cast<const T*>(a.k) + b * a.ks.b + hk * a.ks.h + d0;
-  const T* vbase = reinterpret_cast<const T*>(a.v) + b * a.vs.b + hk * a.vs.h + d0;
 
   for (int g0 = 0; g0 < group; g0 += G) {
     const int h0 = hk * group + g0;
@@ -97,6 +175,9 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const DecodeArgs a) {
     for (int g = 0; g < G; ++g) {
       const T* qp = reinterpret_cast<const T*>(a.q) + b * a.qs.b + (h0 + g) * a.qs.h + d0;
       Vec16<T>::unpack(*reinterpret_cast<const uint4*>(qp), qf[g]);
+      if constexpr (APPEND) {
+        if (rotate) rope_slice<N, LPK, D>(qf[g], a.rope_cos, a.rope_sin, pos, d0, a.rope_interleaved != 0);
+      }
 #pragma unroll
       for (int i = 0; i < N; ++i) qf[g][i] *= c;
     }
@@ -241,18 +322,18 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   if (a.lse && d == 0) a.lse[static_cast<int64_t>(b) * a.Hq + h] = lt > 0.f ? (mn + log2f(lt)) * kLn2 : -INFINITY;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool APPEND>
 cudaError_t launch_t(const DecodeArgs& a, cudaStream_t stream) {
   const int group = a.Hq / a.Hkv;
   dim3 grid(a.nsplit, a.Hkv, a.B);
   if (group % 8 == 0)
-    decode_kernel<T, D, 8><<<grid, kThreads, 0, stream>>>(a);
+    decode_kernel<T, D, 8, APPEND><<<grid, kThreads, 0, stream>>>(a);
   else if (group % 4 == 0)
-    decode_kernel<T, D, 4><<<grid, kThreads, 0, stream>>>(a);
+    decode_kernel<T, D, 4, APPEND><<<grid, kThreads, 0, stream>>>(a);
   else if (group % 2 == 0)
-    decode_kernel<T, D, 2><<<grid, kThreads, 0, stream>>>(a);
+    decode_kernel<T, D, 2, APPEND><<<grid, kThreads, 0, stream>>>(a);
   else
-    decode_kernel<T, D, 1><<<grid, kThreads, 0, stream>>>(a);
+    decode_kernel<T, D, 1, APPEND><<<grid, kThreads, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || a.nsplit == 1) return e;
   decode_combine_kernel<T, D><<<dim3(a.Hq, a.B), D, 0, stream>>>(a);
@@ -270,10 +351,21 @@ void decode_plan(int capacity, int* nsplit, int* chunk) {
   *nsplit = capacity <= ck ? 1 : (capacity + ck - 1) / ck;
 }
 
+template <bool APPEND>
+cudaError_t launch_d(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
+  if (dtype == TT_ATTN_F32)
+    return D == 64 ? launch_t<float, 64, APPEND>(a, stream) : launch_t<float, 128, APPEND>(a, stream);
+  if (dtype == TT_ATTN_F16)
+    return D == 64 ? launch_t<__half, 64, APPEND>(a, stream) : launch_t<__half, 128, APPEND>(a, stream);
+  return D == 64 ? launch_t<__nv_bfloat16, 64, APPEND>(a, stream) : launch_t<__nv_bfloat16, 128, APPEND>(a, stream);
+}
+
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
-  if (dtype == TT_ATTN_F32) return D == 64 ? launch_t<float, 64>(a, stream) : launch_t<float, 128>(a, stream);
-  if (dtype == TT_ATTN_F16) return D == 64 ? launch_t<__half, 64>(a, stream) : launch_t<__half, 128>(a, stream);
-  return D == 64 ? launch_t<__nv_bfloat16, 64>(a, stream) : launch_t<__nv_bfloat16, 128>(a, stream);
+  return launch_d<false>(dtype, D, a, stream);
+}
+
+cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
+  return launch_d<true>(dtype, D, a, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -194,5 +194,55 @@ def sdpAttentionDecode(q, kCache, vCache, kvLens=None, scale=None, needLse=False
     return o, lse
 
 
+def ropeTables(positions, D, theta=10000.0, device="cuda"):
+    """cos / sin tables [positions, D/2] fp32 of the usual rotary embedding: pair i at
+    position p turns by p * theta^(-2i/D)."""
+    inv = theta ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)
+    ang = torch.arange(positions, dtype=torch.float64)[:, None] * inv[None, :]
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+def sdpAttentionDecodeAppend(q, kNew, vNew, kCache, vCache, kvLens, ropeCos=None, ropeSin=None, interleaved=False,
+                             scale=None, needLse=False, status=None):
+    """One step of a token loop: rotate q and kNew to position kvLens[b], write kNew / vNew
+    into row kvLens[b] of the caches (in place), attend over rows [0, kvLens[b]].
+    Returns (O [B,Hq,1,D], LSE or None, newLens = kvLens + 1)."""
+    for t, n in ((q, "q"), (kNew, "kNew"), (vNew, "vNew"), (kCache, "kCache"), (vCache, "vCache")):
+        _check_tensor(t, n)
+    B, Hq, L, D = q.shape
+    _, Hkv, cap, _ = kCache.shape
+    if L != 1 or kNew.shape != (B, Hkv, 1, D) or vNew.shape != (B, Hkv, 1, D):
+        raise ValueError("decode-append takes one query and one new key / value row per sequence")
+    if kvLens is None or kvLens.dtype != torch.int32:
+        raise ValueError("kvLens (int32 [B]) is required")
+    o = torch.empty((B, Hq, 1, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if needLse else None
+    new_lens = torch.empty_like(kvLens)
+    p = _capi.DecodeAppendParams()
+    p.struct_size = C.sizeof(_capi.DecodeAppendParams)
+    p.dtype = _DTYPES[q.dtype]
+    p.B, p.Hq, p.Hkv, p.capacity, p.D = B, Hq, Hkv, cap, D
+    p.q, p.k_new, p.v_new = q.data_ptr(), kNew.data_ptr(), vNew.data_ptr()
+    p.k_cache, p.v_cache, p.o = kCache.data_ptr(), vCache.data_ptr(), o.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.q_strides, p.k_new_strides, p.v_new_strides = _strides(q), _strides(kNew), _strides(vNew)
+    p.k_strides, p.v_strides, p.o_strides = _strides(kCache), _strides(vCache), _strides(o)
+    p.scale = default_scale(D) if scale is None else float(scale)
+    p.kv_lens = kvLens.data_ptr()
+    p.new_lens = new_lens.data_ptr()
+    if ropeCos is not None:
+        if ropeCos.dtype != torch.float32 or ropeCos.shape != ropeSin.shape or ropeCos.shape[1] != D // 2 \
+                or not ropeCos.is_contiguous() or not ropeSin.is_contiguous():
+            raise ValueError("rope tables must be contiguous fp32 [positions, D/2]")
+        p.rope_cos, p.rope_sin = ropeCos.data_ptr(), ropeSin.data_ptr()
+        p.rope_positions = ropeCos.shape[0]
+    p.rope_interleaved = 1 if interleaved else 0
+    _common(p, q)
+    if status is not None:
+        p.status = status.data_ptr()
+    _capi.check(_capi.lib().tt_attn_decode_append(C.byref(p)))
+    return o, lse, new_lens
+
+
 def workspaceBytes(kind, dtype, B, Hq, Hkv, Lq, Skv, D):
     return int(_capi.lib().tt_attn_workspace_bytes(kind, _DTYPES[dtype], B, Hq, Hkv, Lq, Skv, D))

@@ -105,7 +105,15 @@ using SDPAttentionBwdOpFn = TensorList (*)(const Tensor& dO, const Tensor& q, co
 using SDPAttentionDecodeOpFn = Tensor (*)(const Tensor& q, const Tensor& kCache, const Tensor& vCache,
                                           const Tensor& kvLens, float scale);
 
+// one step of a token loop: rotary embedding of q / kNew at position kvLens[b], append of kNew / vNew to the
+// caches (in place), attention over the appended cache; returns {O, kvLens + 1}
+using SDPAttentionDecodeAppendOpFn = TensorPair (*)(const Tensor& q, const Tensor& kNew, const Tensor& vNew,
+                                                    const Tensor& kCache, const Tensor& vCache, const Tensor& kvLens,
+                                                    const Tensor& ropeCos, const Tensor& ropeSin, bool interleaved,
+                                                    float scale);
+
 DEFINE_OP(sdpAttentionFwd, SDPAttentionFwdOpFn)
+DEFINE_OP(sdpAttentionDecodeAppend, SDPAttentionDecodeAppendOpFn)
 DEFINE_OP(sdpAttentionBwd, SDPAttentionBwdOpFn)
 DEFINE_OP(sdpAttentionDecode, SDPAttentionDecodeOpFn)
 
@@ -189,11 +197,46 @@ inline Tensor sdpAttentionDecodeCudaImpl(const Tensor& q, const Tensor& kCache, 
   return o;
 }
 
+inline TensorPair sdpAttentionDecodeAppendCudaImpl(const Tensor& q, const Tensor& kNew, const Tensor& vNew,
+                                                   const Tensor& kCache, const Tensor& vCache, const Tensor& kvLens,
+                                                   const Tensor& ropeCos, const Tensor& ropeSin, bool interleaved,
+                                                   float scale) {
+  const int device = q.device().index;
+  ASSERT(q.size(2) == 1 && kNew.size(2) == 1 && vNew.size(2) == 1 && kvLens.defined());
+  Tensor o(q.shape(), q.options().noGrad());
+  Tensor newLens(kvLens.shape(), kvLens.options().noGrad());
+  tt_attn_decode_append_params p{};
+  p.struct_size = sizeof(p);
+  p.dtype = static_cast<int32_t>(q.dtype());
+  p.B = static_cast<int32_t>(q.size(0)), p.Hq = static_cast<int32_t>(q.size(1));
+  p.Hkv = static_cast<int32_t>(kCache.size(1)), p.capacity = static_cast<int32_t>(kCache.size(2));
+  p.D = static_cast<int32_t>(q.size(3));
+  p.q = q.dataPtr<>(), p.k_new = kNew.dataPtr<>(), p.v_new = vNew.dataPtr<>();
+  p.k_cache = kCache.dataPtr<>(), p.v_cache = vCache.dataPtr<>(), p.o = o.dataPtr<>();
+  p.q_strides = fused_detail::denseStrides(q), p.o_strides = fused_detail::denseStrides(o);
+  p.k_new_strides = fused_detail::denseStrides(kNew), p.v_new_strides = fused_detail::denseStrides(vNew);
+  p.k_strides = fused_detail::denseStrides(kCache), p.v_strides = fused_detail::denseStrides(vCache);
+  p.scale = scale;
+  p.kv_lens = kvLens.dataPtr<int32_t>();
+  p.new_lens = newLens.dataPtr<int32_t>();
+  if (ropeCos.defined()) {
+    p.rope_cos = ropeCos.dataPtr<float>(), p.rope_sin = ropeSin.dataPtr<float>();
+    p.rope_positions = static_cast<int32_t>(ropeCos.size(0));
+  }
+  p.rope_interleaved = interleaved ? 1 : 0;
+  p.device = device;
+  p.stream = cuda::getCurrentCUDAStream(device).stream();
+  p.alloc = fused_detail::allocHook();
+  fused_detail::check(tt_attn_decode_append(&p));
+  return {o, newLens};
+}
+
 inline void registerFusedAttentionCuda() {
   const std::vector<DispatchDType> floats = {DispatchDType::Float32, DispatchDType::Float16, DispatchDType::BFloat16};
   REGISTER_OP_IMPL_MULTI(sdpAttentionFwd, {DispatchDevice::CUDA}, floats, &sdpAttentionFwdCudaImpl);
   REGISTER_OP_IMPL_MULTI(sdpAttentionBwd, {DispatchDevice::CUDA}, floats, &sdpAttentionBwdCudaImpl);
   REGISTER_OP_IMPL_MULTI(sdpAttentionDecode, {DispatchDevice::CUDA}, floats, &sdpAttentionDecodeCudaImpl);
+  REGISTER_OP_IMPL_MULTI(sdpAttentionDecodeAppend, {DispatchDevice::CUDA}, floats, &sdpAttentionDecodeAppendCudaImpl);
 }
 STATIC_CALL(registerFusedAttentionCuda);
 
