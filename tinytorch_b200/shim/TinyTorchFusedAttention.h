@@ -212,7 +212,9 @@ inline TensorPair sdpAttentionDecodeAppendCudaImpl(const Tensor& q, const Tensor
   p.Hkv = static_cast<int32_t>(kCache.size(1)), p.capacity = static_cast<int32_t>(kCache.size(2));
   p.D = static_cast<int32_t>(q.size(3));
   p.q = q.dataPtr<>(), p.k_new = kNew.dataPtr<>(), p.v_new = vNew.dataPtr<>();
-  p.k_cache = kCache.dataPtr<>(), p.v_cache = vCache.dataPtr<>(), p.o = o.dataPtr<>();
+  // the caches are updated in place (as the reference's *Inplace ops do through a const Tensor&)
+  p.k_cache = const_cast<void*>(kCache.dataPtr<>()), p.v_cache = const_cast<void*>(vCache.dataPtr<>());
+  p.o = o.dataPtr<>();
   p.q_strides = fused_detail::denseStrides(q), p.o_strides = fused_detail::denseStrides(o);
   p.k_new_strides = fused_detail::denseStrides(kNew), p.v_new_strides = fused_detail::denseStrides(vNew);
   p.k_strides = fused_detail::denseStrides(kCache), p.v_strides = fused_detail::denseStrides(vCache);
