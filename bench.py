@@ -41,6 +41,10 @@ WORKLOADS = {
     # the fused decode step: rotary embedding + cache append + attention (same bytes, one more row per sequence)
     "decode_append": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0,
                           append=True),
+    # the reference's two fused transformer-block operators (HBM bound): 32768 tokens x hidden 8192,
+    # and a gated MLP of width 14336 over 16384 tokens
+    "rmsnorm": dict(kind="fused", opname="fusedAddRmsNorm", dtype="bf16", rows=32768, dim=8192),
+    "silumul": dict(kind="fused", opname="siluMul", dtype="bf16", rows=16384, dim=14336),
     "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
@@ -388,6 +392,148 @@ def run_ours(args, w, wname):
         dist.destroy_process_group()
 
 
+def run_fused(args, w, wname):
+    """fusedAddRmsNorm / siluMul: GB/s over the algorithmic bytes (every tensor crosses HBM once)."""
+    import torch
+    import torch.distributed as dist
+    from tinytorch_b200 import fused as F
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fused ops have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rows, dim, es = w["rows"], w["dim"], ESIZE[w["dtype"]]
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[w["dtype"]]
+    g = torch.Generator(device=dev).manual_seed(4321 + rank)
+    rms = w["opname"] == "fusedAddRmsNorm"
+    if rms:
+        a = torch.randn((rows, dim), generator=g, device=dev).to(tdt)
+        b = torch.randn((rows, dim), generator=g, device=dev).to(tdt)
+        wt = torch.ones(dim, device=dev, dtype=tdt)
+        fn = lambda: F.fusedAddRmsNorm(a, b, wt, 1e-5)
+        nbytes = float(4 * rows * dim * es + dim * es)  # read input, residual; write both; weight once
+        h2d, d2h = 2 * rows * dim * es, 2 * rows * dim * es
+    else:
+        x = torch.randn((rows, 2 * dim), generator=g, device=dev).to(tdt)
+        fn = lambda: F.siluMul(x)
+        nbytes = float(3 * rows * dim * es)
+        h2d, d2h = 2 * rows * dim * es, rows * dim * es
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(f, steps, warmup):
+        for _ in range(warmup):
+            f()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            f()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / 1e3
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sec = timed(fn, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    per_gpu = nbytes * args.steps / sec / 1e9
+    peaks = measured_peaks()
+    line = {
+        "metric": w["opname"] + " HBM GB/s", "value": per_gpu * world, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic (seeded normal)",
+        "config": {"workload": "%s rows=%d dim=%d %s" % (w["opname"], rows, dim, w["dtype"]),
+                   "l2": "tensors larger than L2 (no flush)", "sharding": "rows per rank, no collective"},
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["gbs"], "unit": "GB/s", "frac": per_gpu / peaks["gbs"],
+                     "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "add_rms_norm_kernel" if rms else "silu_mul_kernel"},
+        "clocks": clocks, "gpu_launches": args.steps,
+    }
+    if not args.no_e2e:
+        # host buffers: pinned H2D of the inputs, the kernel, D2H of what the op produces
+        if rms:
+            ha, hb = (torch.empty((rows, dim), dtype=tdt).pin_memory() for _ in range(2))
+            def e2e():
+                a.copy_(ha, non_blocking=True), b.copy_(hb, non_blocking=True)
+                F.fusedAddRmsNorm(a, b, wt, 1e-5)
+                ha.copy_(a, non_blocking=True), hb.copy_(b, non_blocking=True)
+        else:
+            hx, ho = torch.empty((rows, 2 * dim), dtype=tdt).pin_memory(), torch.empty((rows, dim), dtype=tdt).pin_memory()
+            def e2e():
+                x.copy_(hx, non_blocking=True)
+                ho.copy_(F.siluMul(x), non_blocking=True)
+        n2 = max(3, args.steps // 4)
+        sec2 = timed(e2e, n2, 2)
+        line["e2e"] = {"value": nbytes * n2 / sec2 / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": d2h}
+    if rank == 0 and not args.no_cpu:
+        line["cpu_baseline"] = fused_cpu_sample(w)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def fused_cpu_sample(w, budget_rows=None):
+    """The reference's own CPU code (oracle/_ref) or the C port on a bounded slice of the rows, one core."""
+    from oracle.loader import FusedOracle, Reference
+    ref = Reference() if Reference.available() else FusedOracle()
+    kind = "reference" if Reference.available() else "port"
+    rows = budget_rows or max(1, min(w["rows"], (1 << 28) // (w["dim"] * 4 * 4)))  # ~256 MB of fp32 traffic
+    rng = np.random.default_rng(9)
+    es = ESIZE[w["dtype"]]
+    if w["opname"] == "fusedAddRmsNorm":
+        a, b = (rng.standard_normal((rows, w["dim"]), dtype=np.float32) for _ in range(2))
+        wt = np.ones(w["dim"], dtype=np.float32)
+        t0 = time.perf_counter()
+        ref.fused_add_rms_norm(a, b, wt, 1e-5)
+        dt = time.perf_counter() - t0
+        nbytes = 4 * rows * w["dim"] * es
+    else:
+        x = rng.standard_normal((rows, 2 * w["dim"]), dtype=np.float32)
+        t0 = time.perf_counter()
+        ref.silu_mul(x)
+        dt = time.perf_counter() - t0
+        nbytes = 3 * rows * w["dim"] * es
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+            "sample": "%d of %d rows, fp32 on the host, bytes counted at the workload's dtype" % (rows, w["rows"])}
+
+
+def run_fused_reference_arm(args, w, wname):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup + args.steps):
+        vals.append(fused_cpu_sample(w, budget_rows=max(1, (1 << 26) // (w["dim"] * 4 * 4))))
+    vals = vals[args.warmup:]
+    v = float(np.mean([x["value"] for x in vals]))
+    cb = dict(vals[0], value=v)
+    print(json.dumps({
+        "impl": "reference", "metric": w["opname"] + " HBM GB/s", "value": v, "unit": "GB/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded normal)",
+        "config": {"workload": "%s rows=%d dim=%d (bounded sample per step)" % (w["opname"], w["rows"], w["dim"])},
+        "cpu_baseline": cb, "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -400,7 +546,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if w["kind"] == "fused":
+        (run_fused_reference_arm if args.impl == "reference" else run_fused)(args, w, args.workload)
+    elif args.impl == "reference":
         run_reference_arm(args, w, args.workload)
     else:
         run_ours(args, w, args.workload)

@@ -101,6 +101,31 @@ class Oracle:
         return dq, dk, dv
 
 
+class FusedOracle:
+    """fused_oracle.c: the reference's CPU fp32 siluMul / fusedAddRmsNorm, restated."""
+
+    def __init__(self):
+        self.lib = C.CDLL(ORACLE_SO)
+        self.lib.oracle_silu_mul.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        self.lib.oracle_silu_mul.restype = None
+        self.lib.oracle_fused_add_rms_norm.argtypes = [C.c_void_p] * 3 + [C.c_int64, C.c_int64, C.c_float]
+        self.lib.oracle_fused_add_rms_norm.restype = None
+
+    def silu_mul(self, x):
+        x = _f32(x)
+        rows, last = int(np.prod(x.shape[:-1])), x.shape[-1]
+        out = np.empty(x.shape[:-1] + (last // 2,), dtype=np.float32)
+        self.lib.oracle_silu_mul(_ptr(x), rows, last, _ptr(out))
+        return out
+
+    def fused_add_rms_norm(self, inp, residual, weight, eps):
+        """Returns (new input, new residual); the arguments are not modified."""
+        inp, residual, weight = _f32(inp).copy(), _f32(residual).copy(), _f32(weight)
+        dim = inp.shape[-1]
+        self.lib.oracle_fused_add_rms_norm(_ptr(inp), _ptr(residual), _ptr(weight), inp.size // dim, dim, float(eps))
+        return inp, residual
+
+
 class Reference:
     """The reference's own CPU code.  Single-threaded, like the reference."""
 
@@ -149,6 +174,21 @@ class Reference:
         self.lib.ref_sdpa_fwd_mask(_ptr(q), _ptr(k), _ptr(v), B, H, L, S, D, _ptr(m4), int(is_float), shape,
                                    float(scale) if scale is not None else 0.0, _ptr(out))
         return out
+
+    def silu_mul(self, x):
+        x = _f32(x)
+        rows, last = int(np.prod(x.shape[:-1])), x.shape[-1]
+        out = np.empty(x.shape[:-1] + (last // 2,), dtype=np.float32)
+        self.lib.ref_silu_mul.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        self.lib.ref_silu_mul(_ptr(x), rows, last, _ptr(out))
+        return out
+
+    def fused_add_rms_norm(self, inp, residual, weight, eps):
+        inp, residual, weight = _f32(inp).copy(), _f32(residual).copy(), _f32(weight)
+        dim = inp.shape[-1]
+        self.lib.ref_fused_add_rms_norm.argtypes = [C.c_void_p] * 3 + [C.c_int64, C.c_int64, C.c_float]
+        self.lib.ref_fused_add_rms_norm(_ptr(inp), _ptr(residual), _ptr(weight), inp.size // dim, dim, float(eps))
+        return inp, residual
 
     def grad(self, q, k, v, dout, causal=False, scale=None):
         q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)

@@ -13,6 +13,8 @@
  *                           src/Function/FuncActivation.h:42-63
  *   ref_sdpa_fwd_mask       function::sdpAttention with an attnMask of any broadcastable
  *                           shape, Bool or Float32      src/Function/FuncNNLayer.h:249-256
+ *   ref_silu_mul            op::siluMul                 src/Operation/OpFused.h:19, OpFusedCpu.h:14-39
+ *   ref_fused_add_rms_norm  op::fusedAddRmsNorm         src/Operation/OpFused.h:22, OpFusedCpu.h:42-72
  *   ref_repeat_interleave   op::repeatInterleave        src/Operation/OpTransform.h:168
  *   ref_lse                 op::logSoftmax on the scaled, biased scores the
  *                           forward builds              src/Function/FuncNNLayer.h:237-260
@@ -154,6 +156,26 @@ int ref_sdpa_fwd_mask(const float* q, const float* k, const float* v, int64_t B,
   return 0;
 }
 
-int ref_abi_version(void) { return 2; }
+/* x [rows, last] fp32 -> out [rows, last/2] */
+int ref_silu_mul(const float* x, int64_t rows, int64_t last, float* out) {
+  NoGradGuard guard;
+  Tensor y = op::siluMul(fromHost(x, {rows, last}));
+  toHost(y, out);
+  return 0;
+}
+
+/* in place on input / residual [rows, dim] */
+int ref_fused_add_rms_norm(float* input, float* residual, const float* weight, int64_t rows, int64_t dim, float eps) {
+  NoGradGuard guard;
+  Tensor ti = fromHost(input, {rows, dim});
+  Tensor tr = fromHost(residual, {rows, dim});
+  Tensor tw = fromHost(weight, {dim});
+  op::fusedAddRmsNorm(ti, tr, tw, eps);
+  toHost(ti, input);
+  toHost(tr, residual);
+  return 0;
+}
+
+int ref_abi_version(void) { return 3; }
 
 }  // extern "C"

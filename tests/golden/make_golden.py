@@ -12,6 +12,8 @@ Outputs (both committed):
                            code computes for them here
   ref_seeded.npz           seeded inputs and the reference's outputs for small
                            causal fwd+bwd, length-masked decode and GQA cases
+  ref_seeded_fused.npz     seeded inputs and the reference's outputs of op::siluMul and
+                           op::fusedAddRmsNorm (src/Operation/OpFusedCpu.h:14-72)
   ref_seeded_mask.npz      the same for attnMask: a Bool mask [B,1,L,S] and a float
                            mask [L,S] (src/Function/FuncNNLayer.h:249-256)
 """
@@ -99,6 +101,17 @@ def main():
     np.savez_compressed(os.path.join(HERE, "ref_seeded_mask.npz"), q=Q, k=K, v=V, mask_bool=mb, mask_float=mf,
                         o_bool=ref.fwd_mask(Q, K, V, mb), o_float=ref.fwd_mask(Q, K, V, mf),
                         o_float_scale=ref.fwd_mask(Q, K, V, mf, scale=0.2))
+
+    # --- the two fused transformer-block operators
+    rng = np.random.default_rng(20240609)
+    x = (rng.standard_normal((3, 5, 176)) * 2).astype(np.float32)
+    inp = rng.standard_normal((7, 200)).astype(np.float32)
+    res = rng.standard_normal((7, 200)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(200)).astype(np.float32)
+    n_in, n_res = ref.fused_add_rms_norm(inp, res, w, 1e-5)
+    np.savez_compressed(os.path.join(HERE, "ref_seeded_fused.npz"), silu_x=x, silu_out=ref.silu_mul(x),
+                        rms_input=inp, rms_residual=res, rms_weight=w, rms_eps=np.float32(1e-5),
+                        rms_out_input=n_in, rms_out_residual=n_res)
     print("wrote", os.listdir(HERE))
 
 

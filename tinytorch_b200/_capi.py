@@ -95,6 +95,23 @@ class DecodeAppendParams(C.Structure):
     ]
 
 
+class AddRmsNormParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("rows", C.c_int64), ("dim", C.c_int64),
+        ("input", C.c_void_p), ("residual", C.c_void_p), ("weight", C.c_void_p),
+        ("eps", C.c_float), ("device", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
+class SiluMulParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("rows", C.c_int64), ("d", C.c_int64),
+        ("x", C.c_void_p), ("out", C.c_void_p), ("device", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
+FUSED_EXPORTS = ("tt_fused_add_rms_norm", "tt_silu_mul")  # include/tt_fused.h
+
 EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_append", "tt_attn_decode_static", "tt_attn_workspace_bytes", "tt_attn_strerror",
            "tt_attn_last_cuda_error", "tt_attn_version")
 
@@ -121,6 +138,10 @@ def lib():
         L.tt_attn_decode.argtypes = [C.POINTER(DecodeParams)]
         L.tt_attn_decode_append.argtypes = [C.POINTER(DecodeAppendParams)]
         L.tt_attn_decode_append.restype = C.c_int
+        L.tt_fused_add_rms_norm.argtypes = [C.POINTER(AddRmsNormParams)]
+        L.tt_fused_add_rms_norm.restype = C.c_int
+        L.tt_silu_mul.argtypes = [C.POINTER(SiluMulParams)]
+        L.tt_silu_mul.restype = C.c_int
         L.tt_attn_decode_static.argtypes = [C.POINTER(DecodeParams)]
         L.tt_attn_decode_static.restype = C.c_int
         for n in ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_version"):

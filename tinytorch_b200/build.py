@@ -27,6 +27,7 @@ def _sources():
 def _headers_mtime():
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     hs.append(os.path.join(HERE, "..", "include", "tt_attn.h"))
+    hs.append(os.path.join(HERE, "..", "include", "tt_fused.h"))
     return max(os.path.getmtime(h) for h in hs)
 
 

@@ -5,7 +5,9 @@
 #include <cstdio>
 #include <cstring>
 
+#include "../../include/tt_fused.h"
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace ttattn {
 namespace {
@@ -321,6 +323,39 @@ int tt_attn_decode_static(const tt_attn_decode_params* p) {
   cudaError_t e =
       launch_decode_static(p->dtype, p->D, a, need, p->device, static_cast<cudaStream_t>(p->stream), &too_large);
   if (too_large) return TT_ATTN_ERR_TOO_LARGE;
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
+int tt_fused_add_rms_norm(const tt_fused_add_rms_norm_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_fused_add_rms_norm_params)) return TT_ATTN_ERR_STRUCT;
+  if (p->dtype < TT_ATTN_F32 || p->dtype > TT_ATTN_BF16) return TT_ATTN_ERR_DTYPE;
+  if (p->rows < 0 || p->dim <= 0 || p->rows > 0x7fffffff) return TT_ATTN_ERR_SHAPE;
+  if (p->rows == 0) return TT_ATTN_OK;  // an empty tensor has no storage to point to
+  if (!p->input || !p->residual || !p->weight) return TT_ATTN_ERR_NULL;
+  const size_t es = elem_size(p->dtype);
+  if (reinterpret_cast<uintptr_t>(p->input) % es || reinterpret_cast<uintptr_t>(p->residual) % es ||
+      reinterpret_cast<uintptr_t>(p->weight) % es)
+    return TT_ATTN_ERR_ALIGN;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  cudaError_t e = launch_fused_add_rms_norm(p->dtype, p->input, p->residual, p->weight, p->rows, p->dim, p->eps,
+                                            static_cast<cudaStream_t>(p->stream));
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
+int tt_silu_mul(const tt_silu_mul_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_silu_mul_params)) return TT_ATTN_ERR_STRUCT;
+  if (p->dtype < TT_ATTN_F32 || p->dtype > TT_ATTN_BF16) return TT_ATTN_ERR_DTYPE;
+  if (p->rows < 0 || p->d <= 0) return TT_ATTN_ERR_SHAPE;
+  if (p->rows == 0) return TT_ATTN_OK;
+  if (!p->x || !p->out) return TT_ATTN_ERR_NULL;
+  const size_t es = elem_size(p->dtype);
+  if (reinterpret_cast<uintptr_t>(p->x) % es || reinterpret_cast<uintptr_t>(p->out) % es) return TT_ATTN_ERR_ALIGN;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  cudaError_t e = launch_silu_mul(p->dtype, p->out, p->x, p->rows, p->d, static_cast<cudaStream_t>(p->stream));
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
 

@@ -110,6 +110,11 @@ cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStre
 cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, int device, cudaStream_t stream,
                                  bool* too_large);
 
+// The reference's two fused transformer-block operators (fused_ops.cu).
+cudaError_t launch_fused_add_rms_norm(int dtype, void* input, void* residual, const void* weight, int64_t rows,
+                                      int64_t dim, float eps, cudaStream_t stream);
+cudaError_t launch_silu_mul(int dtype, void* out, const void* x, int64_t rows, int64_t d, cudaStream_t stream);
+
 // Split planning for decode, shared by the launcher and the workspace query.
 void decode_plan(int capacity, int* nsplit, int* chunk);
 
