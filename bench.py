@@ -45,6 +45,11 @@ WORKLOADS = {
     # and a gated MLP of width 14336 over 16384 tokens
     "rmsnorm": dict(kind="fused", opname="fusedAddRmsNorm", dtype="bf16", rows=32768, dim=8192),
     "silumul": dict(kind="fused", opname="siluMul", dtype="bf16", rows=16384, dim=14336),
+    # reduced copies for profiler captures (a few hundred MB, still larger than L2)
+    "rmsnorm_ncu": dict(kind="fused", opname="fusedAddRmsNorm", dtype="bf16", rows=8192, dim=8192),
+    "silumul_ncu": dict(kind="fused", opname="siluMul", dtype="bf16", rows=4096, dim=14336),
+    "decode_append_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0,
+                              append=True),
     "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
