@@ -50,6 +50,9 @@ WORKLOADS = {
     "silumul_ncu": dict(kind="fused", opname="siluMul", dtype="bf16", rows=4096, dim=14336),
     "decode_append_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0,
                               append=True),
+    # the QKV projection in front of attention: 16384 tokens, hidden 4096 -> 3 x 4096 (tensor bound)
+    "linear": dict(kind="fused", opname="linear", dtype="bf16", rows=16384, dim=4096, n_out=12288),
+    "linear_ncu": dict(kind="fused", opname="linear", dtype="bf16", rows=4096, dim=4096, n_out=4096),
     "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
@@ -416,7 +419,15 @@ def run_fused(args, w, wname):
     tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[w["dtype"]]
     g = torch.Generator(device=dev).manual_seed(4321 + rank)
     rms = w["opname"] == "fusedAddRmsNorm"
-    if rms:
+    lin = w["opname"] == "linear"
+    if lin:
+        x = (torch.randn((rows, dim), generator=g, device=dev) * 0.5).to(tdt)
+        wt = (torch.randn((w["n_out"], dim), generator=g, device=dev) * 0.05).to(tdt)
+        bs = torch.randn((w["n_out"],), generator=g, device=dev).to(tdt)
+        fn = lambda: F._linear_raw(x, wt, bs)
+        nbytes = 2.0 * rows * dim * w["n_out"]  # FLOPs for this operator
+        h2d, d2h = rows * dim * es, rows * w["n_out"] * es
+    elif rms:
         a = torch.randn((rows, dim), generator=g, device=dev).to(tdt)
         b = torch.randn((rows, dim), generator=g, device=dev).to(tdt)
         wt = torch.ones(dim, device=dev, dtype=tdt)
@@ -456,22 +467,31 @@ def run_fused(args, w, wname):
         sampler.start()
     sec = timed(fn, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    per_gpu = nbytes * args.steps / sec / 1e9
+    div, unit = (1e12, "TFLOP/s") if lin else (1e9, "GB/s")
+    per_gpu = nbytes * args.steps / sec / div
     peaks = measured_peaks()
+    peak = peaks["tflops"] if lin else peaks["gbs"]
     line = {
-        "metric": w["opname"] + " HBM GB/s", "value": per_gpu * world, "unit": "GB/s", "n_gpus": world,
+        "metric": "projection TFLOP/s" if lin else w["opname"] + " HBM GB/s", "value": per_gpu * world, "unit": unit,
+        "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic (seeded normal)",
         "config": {"workload": "%s rows=%d dim=%d %s" % (w["opname"], rows, dim, w["dtype"]),
                    "l2": "tensors larger than L2 (no flush)", "sharding": "rows per rank, no collective"},
-        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["gbs"], "unit": "GB/s", "frac": per_gpu / peaks["gbs"],
-                     "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "add_rms_norm_kernel" if rms else "silu_mul_kernel"},
+        "roofline": {"bound": "tensor" if lin else "hbm", "achieved": per_gpu, "peak": peak, "unit": unit,
+                     "frac": per_gpu / peak, "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "linear_tc_kernel" if lin else ("add_rms_norm_kernel" if rms else "silu_mul_kernel")},
         "clocks": clocks, "gpu_launches": args.steps,
     }
     if not args.no_e2e:
         # host buffers: pinned H2D of the inputs, the kernel, D2H of what the op produces
-        if rms:
+        if lin:
+            hx = torch.empty((rows, dim), dtype=tdt).pin_memory()
+            hy = torch.empty((rows, w["n_out"]), dtype=tdt).pin_memory()
+            def e2e():
+                x.copy_(hx, non_blocking=True)
+                hy.copy_(F._linear_raw(x, wt, bs), non_blocking=True)
+        elif rms:
             ha, hb = (torch.empty((rows, dim), dtype=tdt).pin_memory() for _ in range(2))
             def e2e():
                 a.copy_(ha, non_blocking=True), b.copy_(hb, non_blocking=True)
@@ -484,7 +504,7 @@ def run_fused(args, w, wname):
                 ho.copy_(F.siluMul(x), non_blocking=True)
         n2 = max(3, args.steps // 4)
         sec2 = timed(e2e, n2, 2)
-        line["e2e"] = {"value": nbytes * n2 / sec2 / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+        line["e2e"] = {"value": nbytes * n2 / sec2 / div * world, "unit": unit, "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": d2h}
     if rank == 0 and not args.no_cpu:
         line["cpu_baseline"] = fused_cpu_sample(w)
@@ -502,6 +522,16 @@ def fused_cpu_sample(w, budget_rows=None):
     rows = budget_rows or max(1, min(w["rows"], (1 << 28) // (w["dim"] * 4 * 4)))  # ~256 MB of fp32 traffic
     rng = np.random.default_rng(9)
     es = ESIZE[w["dtype"]]
+    if w["opname"] == "linear":
+        rows = budget_rows or 8  # 8 rows x 4096 x 12288 = 0.8 GFLOP of the reference's scalar gemm
+        x = rng.standard_normal((rows, w["dim"]), dtype=np.float32)
+        wt = rng.standard_normal((w["n_out"], w["dim"]), dtype=np.float32)
+        bs = rng.standard_normal(w["n_out"], dtype=np.float32)
+        t0 = time.perf_counter()
+        ref.linear(x, wt, bs)
+        dt = time.perf_counter() - t0
+        return {"value": 2.0 * rows * w["dim"] * w["n_out"] / dt / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
+                "sample": "%d of %d rows, fp32 on the host" % (rows, w["rows"])}
     if w["opname"] == "fusedAddRmsNorm":
         a, b = (rng.standard_normal((rows, w["dim"]), dtype=np.float32) for _ in range(2))
         wt = np.ones(w["dim"], dtype=np.float32)
@@ -525,17 +555,18 @@ def run_fused_reference_arm(args, w, wname):
         return
     vals = []
     for _ in range(args.warmup + args.steps):
-        vals.append(fused_cpu_sample(w, budget_rows=max(1, (1 << 26) // (w["dim"] * 4 * 4))))
+        vals.append(fused_cpu_sample(w, budget_rows=4 if w["opname"] == "linear" else max(1, (1 << 26) // (w["dim"] * 4 * 4))))
     vals = vals[args.warmup:]
     v = float(np.mean([x["value"] for x in vals]))
     cb = dict(vals[0], value=v)
     print(json.dumps({
-        "impl": "reference", "metric": w["opname"] + " HBM GB/s", "value": v, "unit": "GB/s",
+        "impl": "reference", "metric": "projection TFLOP/s" if w["opname"] == "linear" else w["opname"] + " HBM GB/s",
+        "value": v, "unit": vals[0]["unit"],
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded normal)",
         "config": {"workload": "%s rows=%d dim=%d (bounded sample per step)" % (w["opname"], w["rows"], w["dim"])},
-        "cpu_baseline": cb, "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": cb, "e2e": {"value": v, "unit": vals[0]["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 

@@ -111,6 +111,17 @@ class FusedOracle:
         self.lib.oracle_fused_add_rms_norm.argtypes = [C.c_void_p] * 3 + [C.c_int64, C.c_int64, C.c_float]
         self.lib.oracle_fused_add_rms_norm.restype = None
 
+    def linear(self, x, w, bias=None):
+        x, w = _f32(x), _f32(w)
+        bias = _f32(bias) if bias is not None else None
+        M, K = x.shape
+        N = w.shape[0]
+        y = np.empty((M, N), dtype=np.float32)
+        self.lib.oracle_linear.argtypes = [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p]
+        self.lib.oracle_linear.restype = None
+        self.lib.oracle_linear(_ptr(x), _ptr(w), _ptr(bias), M, N, K, _ptr(y))
+        return y
+
     def silu_mul(self, x):
         x = _f32(x)
         rows, last = int(np.prod(x.shape[:-1])), x.shape[-1]
@@ -189,6 +200,25 @@ class Reference:
         self.lib.ref_fused_add_rms_norm.argtypes = [C.c_void_p] * 3 + [C.c_int64, C.c_int64, C.c_float]
         self.lib.ref_fused_add_rms_norm(_ptr(inp), _ptr(residual), _ptr(weight), inp.size // dim, dim, float(eps))
         return inp, residual
+
+    def linear(self, x, w, bias=None):
+        x, w = _f32(x), _f32(w)
+        bias = _f32(bias) if bias is not None else None
+        M, K = x.shape
+        N = w.shape[0]
+        y = np.empty((M, N), dtype=np.float32)
+        self.lib.ref_linear.argtypes = [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p]
+        self.lib.ref_linear(_ptr(x), _ptr(w), _ptr(bias), M, N, K, _ptr(y))
+        return y
+
+    def linear_grad(self, x, w, bias, dy):
+        x, w, bias, dy = _f32(x), _f32(w), _f32(bias), _f32(dy)
+        M, K = x.shape
+        N = w.shape[0]
+        dx, dw, db = np.empty_like(x), np.empty_like(w), np.empty_like(bias)
+        self.lib.ref_linear_grad.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 3 + [C.c_void_p] * 3
+        self.lib.ref_linear_grad(_ptr(x), _ptr(w), _ptr(bias), _ptr(dy), M, N, K, _ptr(dx), _ptr(dw), _ptr(db))
+        return dx, dw, db
 
     def grad(self, q, k, v, dout, causal=False, scale=None):
         q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)

@@ -15,6 +15,8 @@
  *                           shape, Bool or Float32      src/Function/FuncNNLayer.h:249-256
  *   ref_silu_mul            op::siluMul                 src/Operation/OpFused.h:19, OpFusedCpu.h:14-39
  *   ref_fused_add_rms_norm  op::fusedAddRmsNorm         src/Operation/OpFused.h:22, OpFusedCpu.h:42-72
+ *   ref_linear              function::linear            src/Function/FuncNNLayer.h:270-272
+ *   ref_linear_grad         FuncLinear::backward        src/Function/FuncNNLayer.h:20-34
  *   ref_repeat_interleave   op::repeatInterleave        src/Operation/OpTransform.h:168
  *   ref_lse                 op::logSoftmax on the scaled, biased scores the
  *                           forward builds              src/Function/FuncNNLayer.h:237-260
@@ -176,6 +178,30 @@ int ref_fused_add_rms_norm(float* input, float* residual, const float* weight, i
   return 0;
 }
 
-int ref_abi_version(void) { return 3; }
+/* y[M,N] = linear(x[M,K], w[N,K], bias[N] or NULL) */
+int ref_linear(const float* x, const float* w, const float* bias, int64_t M, int64_t N, int64_t K, float* y) {
+  NoGradGuard guard;
+  Tensor tb = bias ? fromHost(bias, {N}) : Tensor{};
+  Tensor ty = function::linear(fromHost(x, {M, K}), fromHost(w, {N, K}), tb);
+  toHost(ty, y);
+  return 0;
+}
+
+/* gradients of linear(x, w, bias) for an upstream gradient dy[M,N] */
+int ref_linear_grad(const float* x, const float* w, const float* bias, const float* dy, int64_t M, int64_t N,
+                    int64_t K, float* dx, float* dw, float* db) {
+  Tensor tx = fromHost(x, {M, K}), tw = fromHost(w, {N, K}), tb = fromHost(bias, {N});
+  tx.setRequiresGrad(true);
+  tw.setRequiresGrad(true);
+  tb.setRequiresGrad(true);
+  Tensor ty = function::linear(tx, tw, tb);
+  ty.backward(fromHost(dy, {M, N}));
+  toHost(tx.grad(), dx);
+  toHost(tw.grad(), dw);
+  toHost(tb.grad(), db);
+  return 0;
+}
+
+int ref_abi_version(void) { return 4; }
 
 }  // extern "C"

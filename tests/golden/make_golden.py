@@ -14,6 +14,9 @@ Outputs (both committed):
                            causal fwd+bwd, length-masked decode and GQA cases
   ref_seeded_fused.npz     seeded inputs and the reference's outputs of op::siluMul and
                            op::fusedAddRmsNorm (src/Operation/OpFusedCpu.h:14-72)
+  ref_seeded_linear.npz    function::linear: the reference's known-answer vectors
+                           (test/test_function.cpp:234-248, asserted here) and a seeded
+                           forward / backward case
   ref_seeded_mask.npz      the same for attnMask: a Bool mask [B,1,L,S] and a float
                            mask [L,S] (src/Function/FuncNNLayer.h:249-256)
 """
@@ -109,6 +112,23 @@ def main():
     res = rng.standard_normal((7, 200)).astype(np.float32)
     w = (1 + 0.1 * rng.standard_normal(200)).astype(np.float32)
     n_in, n_res = ref.fused_add_rms_norm(inp, res, w, 1e-5)
+    # function::linear: the reference's own known answer (test/test_function.cpp:234-248) and a seeded case
+    kx = np.array([[-0.3089, 0.5301, -0.0245], [1.5852, 0.8954, 0.7485]], dtype=np.float32)
+    kw = np.array([[0.8397, 1.7990, -0.2738], [-0.8910, -0.6746, 0.3419]], dtype=np.float32)
+    kb = np.array([-0.9601, -1.4163], dtype=np.float32)
+    ky = ref.linear(kx, kw, kb)
+    assert abs(float(ky.sum()) - (-3.1661377)) <= 1e-5
+    kdx, kdw, kdb = ref.linear_grad(kx, kw, kb, np.ones_like(ky))
+    assert np.abs(kdx.ravel() - [-0.0512999892, 1.1244, 0.0681000054] * 2).max() <= 1e-4
+    assert np.abs(kdw.ravel() - [1.2763, 1.42549992, 0.724] * 2).max() <= 1e-4 and list(kdb) == [2.0, 2.0]
+    lx = rng.standard_normal((37, 72)).astype(np.float32)
+    lw = rng.standard_normal((40, 72)).astype(np.float32)
+    lb = rng.standard_normal(40).astype(np.float32)
+    ldy = rng.standard_normal((37, 40)).astype(np.float32)
+    ldx, ldw, ldb = ref.linear_grad(lx, lw, lb, ldy)
+    np.savez_compressed(os.path.join(HERE, "ref_seeded_linear.npz"), known_x=kx, known_w=kw, known_b=kb, known_y=ky,
+                        x=lx, w=lw, b=lb, y=ref.linear(lx, lw, lb), y_nobias=ref.linear(lx, lw), dy=ldy, dx=ldx, dw=ldw,
+                        db=ldb)
     np.savez_compressed(os.path.join(HERE, "ref_seeded_fused.npz"), silu_x=x, silu_out=ref.silu_mul(x),
                         rms_input=inp, rms_residual=res, rms_weight=w, rms_eps=np.float32(1e-5),
                         rms_out_input=n_in, rms_out_residual=n_res)

@@ -49,6 +49,46 @@ def test_oracle_against_numpy_fp64(fused):
     assert np.abs(n_res - r).max() <= 1e-6 and np.abs(n_in - want).max() <= 1e-5
 
 
+def test_linear_oracle_matches_fixture_and_reference_known_answer(fused):
+    g = np.load(os.path.join(GOLDEN, "ref_seeded_linear.npz"))
+    # the reference's own test vector (test/test_function.cpp:234-241): sum of linear(x, w, b) = -3.1661377
+    y = fused.linear(g["known_x"], g["known_w"], g["known_b"])
+    assert np.array_equal(y, g["known_y"]) and abs(float(y.sum()) + 3.1661377) <= 1e-5
+    assert np.array_equal(fused.linear(g["x"], g["w"], g["b"]), g["y"])
+    assert np.array_equal(fused.linear(g["x"], g["w"]), g["y_nobias"])
+    # gradients of the fixture are those of three more linear maps: dX = dY W, dW = dY^T X, db = column sums
+    assert np.abs(fused.linear(g["dy"], g["w"].T.copy()) - g["dx"]).max() <= 1e-4
+    assert np.abs(fused.linear(g["dy"].T.copy(), g["x"].T.copy()) - g["dw"]).max() <= 1e-4
+    assert np.abs(g["dy"].sum(0) - g["db"]).max() <= 1e-4
+
+
+def test_linear_oracle_live_against_reference(fused, reference):
+    rng = np.random.default_rng(6)
+    x, w, b = rng.standard_normal((9, 50)), rng.standard_normal((13, 50)), rng.standard_normal(13)
+    assert np.array_equal(fused.linear(x, w, b), reference.linear(x, w, b))
+    assert np.array_equal(fused.linear(x, w), reference.linear(x, w))
+
+
+def test_linear_rejects_bad_arguments():
+    lib = _capi.lib()
+    assert lib.tt_linear(None) == -1
+    p = _capi.LinearParams()
+    p.struct_size = C.sizeof(p)
+    p.dtype, p.M, p.N, p.K = 2, 128, 256, 64
+    assert lib.tt_linear(C.byref(p)) == -1            # null tensors
+    p.x = p.w = p.y = 0x1000
+    p.dtype = 0
+    assert lib.tt_linear(C.byref(p)) == -2            # Float32 is not served by this kernel
+    p.dtype, p.K = 2, 60
+    assert lib.tt_linear(C.byref(p)) == -5            # K not a multiple of 8
+    p.K, p.ldx = 64, 32
+    assert lib.tt_linear(C.byref(p)) == -3            # row stride shorter than a row
+    p.ldx, p.N = 0, 0
+    assert lib.tt_linear(C.byref(p)) == -3
+    p.N, p.M = 256, 0
+    assert lib.tt_linear(C.byref(p)) == 0             # nothing to do
+
+
 def test_library_exports_every_symbol_of_tt_fused_h():
     text = open(os.path.join(ROOT, "include", "tt_fused.h")).read()
     names = re.findall(r"TT_ATTN_API\s+[\w\s\*]+?\b(tt_\w+)\s*\(", text)

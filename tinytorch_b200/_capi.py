@@ -110,7 +110,16 @@ class SiluMulParams(C.Structure):
     ]
 
 
-FUSED_EXPORTS = ("tt_fused_add_rms_norm", "tt_silu_mul")  # include/tt_fused.h
+class LinearParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
+        ("x", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("y", C.c_void_p),
+        ("ldx", C.c_int64), ("ldw", C.c_int64), ("ldy", C.c_int64),
+        ("device", C.c_int32), ("stream", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
+FUSED_EXPORTS = ("tt_fused_add_rms_norm", "tt_silu_mul", "tt_linear")  # include/tt_fused.h
 
 EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_append", "tt_attn_decode_static", "tt_attn_workspace_bytes", "tt_attn_strerror",
            "tt_attn_last_cuda_error", "tt_attn_version")
@@ -142,6 +151,8 @@ def lib():
         L.tt_fused_add_rms_norm.restype = C.c_int
         L.tt_silu_mul.argtypes = [C.POINTER(SiluMulParams)]
         L.tt_silu_mul.restype = C.c_int
+        L.tt_linear.argtypes = [C.POINTER(LinearParams)]
+        L.tt_linear.restype = C.c_int
         L.tt_attn_decode_static.argtypes = [C.POINTER(DecodeParams)]
         L.tt_attn_decode_static.restype = C.c_int
         for n in ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_version"):

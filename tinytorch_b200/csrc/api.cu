@@ -359,4 +359,25 @@ int tt_silu_mul(const tt_silu_mul_params* p) {
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
 
+int tt_linear(const tt_linear_params* p) {
+  if (!p) return TT_ATTN_ERR_NULL;
+  if (p->struct_size != sizeof(tt_linear_params)) return TT_ATTN_ERR_STRUCT;
+  if (p->dtype != TT_ATTN_F16 && p->dtype != TT_ATTN_BF16) return TT_ATTN_ERR_DTYPE;
+  if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->M > 0x7fffffff || p->N > 0x7fffffff || p->K > 0x7fffffff)
+    return TT_ATTN_ERR_SHAPE;
+  if (p->M == 0) return TT_ATTN_OK;
+  if (!p->x || !p->w || !p->y) return TT_ATTN_ERR_NULL;
+  const int64_t ldx = p->ldx ? p->ldx : p->K, ldw = p->ldw ? p->ldw : p->K, ldy = p->ldy ? p->ldy : p->N;
+  if (ldx < p->K || ldw < p->K || ldy < p->N) return TT_ATTN_ERR_SHAPE;
+  if (p->K % 8 || p->N % 8 || ldx % 8 || ldw % 8 || ldy % 8 || !aligned16(p->x) || !aligned16(p->w) ||
+      !aligned16(p->y) || (p->bias && reinterpret_cast<uintptr_t>(p->bias) % 2))
+    return TT_ATTN_ERR_ALIGN;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  cudaError_t e = launch_linear_tc(p->dtype, p->x, p->w, p->bias, p->y, static_cast<int>(p->M), static_cast<int>(p->N),
+                                   static_cast<int>(p->K), ldx, ldw, ldy, p->status, p->device,
+                                   static_cast<cudaStream_t>(p->stream));
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
 }  // extern "C"

@@ -14,6 +14,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 // Status bits a kernel may OR into the caller's status word.
 constexpr int kStatusWaitExpired = 1;
+constexpr int kStatusBadSmemAlign = 2;   // dynamic shared memory did not start on a 1024-byte boundary
 constexpr int kStatusCacheFull = 4;      // decode-append: no free row in the cache of some sequence
 constexpr int kStatusRopeRange = 8;      // decode-append: position beyond the rotary tables
 
@@ -114,6 +115,10 @@ cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, in
 cudaError_t launch_fused_add_rms_norm(int dtype, void* input, void* residual, const void* weight, int64_t rows,
                                       int64_t dim, float eps, cudaStream_t stream);
 cudaError_t launch_silu_mul(int dtype, void* out, const void* x, int64_t rows, int64_t d, cudaStream_t stream);
+
+// y = x w^T + bias on the tensor cores (linear_tc.cu); ld* are row strides in elements
+cudaError_t launch_linear_tc(int dtype, const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
+                             int64_t ldx, int64_t ldw, int64_t ldy, int32_t* status, int device, cudaStream_t stream);
 
 // Split planning for decode, shared by the launcher and the workspace query.
 void decode_plan(int capacity, int* nsplit, int* chunk);

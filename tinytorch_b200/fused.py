@@ -6,9 +6,14 @@ reference's names, argument meaning and in-place behaviour:
   fusedAddRmsNorm(input, residual, weight, eps)  op::fusedAddRmsNorm, function::fusedAddRmsNorm
       (src/Operation/OpFused.h:22, src/Function/FuncFused.h:21-28,33-35)
 
-Both go through the C ABI of libtt_attn.so (include/tt_fused.h) and launch on the
-current CUDA stream of the tensors' device.  Neither has a CPU implementation here,
-and - as in the reference (FuncFused.h:18,27) - neither has a backward.
+  linear(input, weight, bias=None)            function::linear
+      (src/Function/FuncNNLayer.h:14-35,270-272): input [..., K] x weight [N, K]^T + bias [N];
+      float16 / bfloat16 on the tensor cores (float32 stays on the library gemm and is refused here),
+      with the reference's backward (dX = dY W, dW = dY^T X, db = sum dY) through the same kernel
+
+All go through the C ABI of libtt_attn.so (include/tt_fused.h) and launch on the
+current CUDA stream of the tensors' device.  None has a CPU implementation here, and - as
+in the reference (FuncFused.h:18,27) - siluMul and fusedAddRmsNorm have no backward.
 """
 import ctypes as C
 
@@ -63,3 +68,71 @@ def fusedAddRmsNorm(input, residual, weight, eps):
     p.device = _dev(input)
     p.stream = torch.cuda.current_stream(p.device).cuda_stream
     _capi.check(_capi.lib().tt_fused_add_rms_norm(C.byref(p)))
+
+
+def _linear_raw(x2, w, bias, status=None):
+    """x2 [M, K] @ w [N, K]^T (+ bias [N]) -> [M, N]; rows may be strided, columns are contiguous."""
+    M, K = x2.shape
+    N = w.shape[0]
+    y = torch.empty((M, N), dtype=x2.dtype, device=x2.device)
+    p = _capi.LinearParams()
+    p.struct_size = C.sizeof(_capi.LinearParams)
+    p.dtype = _DTYPES[x2.dtype]
+    p.M, p.N, p.K = M, N, K
+    p.x, p.w, p.y = x2.data_ptr(), w.data_ptr(), y.data_ptr()
+    p.bias = bias.data_ptr() if bias is not None else None
+    p.ldx, p.ldw, p.ldy = x2.stride(0), w.stride(0), N
+    p.device = _dev(x2)
+    p.stream = torch.cuda.current_stream(p.device).cuda_stream
+    p.status = status.data_ptr() if status is not None else None
+    _capi.check(_capi.lib().tt_linear(C.byref(p)))
+    return y
+
+
+def _check_linear(input, weight, bias):
+    if not input.is_cuda or input.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("linear needs CUDA float16 / bfloat16 tensors (float32 stays on the library gemm; no CPU path)")
+    if weight.dim() != 2 or weight.dtype != input.dtype or weight.device != input.device:
+        raise ValueError("weight must be [N, K] with the dtype and device of input")
+    if input.shape[-1] != weight.shape[1]:
+        raise AssertionError("matmul error: shape not aligned (OpLinalg.cpp:251-254)")
+    if bias is not None and (bias.dim() != 1 or bias.shape[0] != weight.shape[0] or bias.dtype != input.dtype):
+        raise AssertionError("bias must be [N] (OpLinalg.cpp:261-263)")
+
+
+class FuncLinear(torch.autograd.Function):
+    """function::FuncLinear (src/Function/FuncNNLayer.h:14-35) on the tcgen05 kernel."""
+
+    @staticmethod
+    def forward(ctx, input, weight, bias):
+        x2 = input.reshape(-1, input.shape[-1])
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        w = weight if weight.stride(1) == 1 else weight.contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.in_shape = input.shape
+        return _linear_raw(x2, w, bias).reshape(input.shape[:-1] + (weight.shape[0],))
+
+    @staticmethod
+    def backward(ctx, grad):
+        x2, w = ctx.saved_tensors
+        g2 = grad.reshape(-1, grad.shape[-1])
+        if g2.stride(1) != 1:
+            g2 = g2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # dX[M,K] = dY[M,N] W[N,K] = dY (W^T)^T: the kernel contracts over the last dimension of both operands
+            dx = _linear_raw(g2, w.t().contiguous(), None).reshape(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            # dW[N,K] = dY^T[N,M] X[M,K] = (dY^T) (X^T)^T
+            dw = _linear_raw(g2.t().contiguous(), x2.t().contiguous(), None)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = g2.float().sum(0).to(grad.dtype)
+        return dx, dw, db
+
+
+def linear(input, weight, bias=None):
+    """Drop-in for function::linear (src/Function/FuncNNLayer.h:270-272)."""
+    _check_linear(input, weight, bias)
+    return FuncLinear.apply(input, weight, bias)

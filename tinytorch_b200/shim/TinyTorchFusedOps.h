@@ -67,6 +67,31 @@ inline void fusedAddRmsNormOpB200Impl(Tensor& input, Tensor& residual, const Ten
   fusedB200Check(tt_fused_add_rms_norm(&p));
 }
 
+// y = input w^T + bias for CUDA Float16 / BFloat16 tensors whose last dimension is contiguous and whose sizes
+// and row strides are multiples of 8: what FuncLinear::forward (src/Function/FuncNNLayer.h:16-18) gets from
+// op::matmul(input, weight, false, true, bias).  Returns an undefined Tensor when the kernel does not apply, so
+// that the caller falls back to op::matmul.
+inline Tensor linearOpB200(const Tensor& input, const Tensor& weight, const Tensor& bias) {
+  if (!input.device().isCuda() || (input.dtype() != DType::Float16 && input.dtype() != DType::BFloat16)) return {};
+  if (weight.dim() != 2 || weight.dtype() != input.dtype() || input.dim() < 1) return {};
+  const int64_t K = input.size(-1), N = weight.size(0);
+  if (weight.size(1) != K || K % 8 != 0 || N % 8 != 0) return {};
+  if (bias.defined() && (bias.dim() != 1 || bias.size(0) != N || bias.dtype() != input.dtype())) return {};
+  SizeVector retShape = input.shape();
+  retShape.back() = N;
+  auto ret = Tensor::empty(retShape, input.options().noGrad());
+  tt_linear_params p{};
+  p.struct_size = sizeof(p);
+  p.dtype = static_cast<int32_t>(input.dtype());
+  p.K = K, p.N = N, p.M = input.numel() / K;  // tensors are dense: leading dimensions flatten into rows
+  p.x = input.dataPtr<>(), p.w = weight.dataPtr<>(), p.y = ret.dataPtr<>();
+  p.bias = bias.defined() ? bias.dataPtr<>() : nullptr;
+  p.device = input.device().index;
+  p.stream = cuda::getCurrentCUDAStream(input.device().index).stream();
+  fusedB200Check(tt_linear(&p));
+  return ret;
+}
+
 inline void registerFusedOpsB200() {
   const std::vector<DispatchDType> floats = {DispatchDType::Float32, DispatchDType::Float16, DispatchDType::BFloat16};
   REGISTER_OP_IMPL_MULTI(siluMul, {DispatchDevice::CUDA}, floats, &siluMulOpB200Impl);
