@@ -23,8 +23,9 @@
 //                     B = K tile read MN-major)             -> its own TMEM columns
 //                     when D = 64, else region A
 // dV and dK accumulate in TMEM over the whole walk and are written once.  dQ of a
-// (key tile, query tile) pair is added to an fp32 buffer with red.global.add and
-// converted to the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
+// (key tile, query tile) pair is added to an fp32 buffer through swizzled staging
+// tiles and TMA reductions (cp.reduce.async.bulk.tensor ... add) and converted to
+// the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
 // with TMA (128-byte swizzle, one copy per CTA), one thread of warp 17 issues the MMAs;
 // every wait is bounded.
 #include <type_traits>
@@ -40,7 +41,7 @@ constexpr int BM = 128;  // key rows per CTA (= TMEM lanes)
 constexpr int BQ = 128;  // query rows per step
 constexpr int kThreads = 576;  // four compute warpgroups (32 queries of every step each) + producer warp + issuer warp
 constexpr int kCompute = 512;
-constexpr int kReaders = 256;  // warpgroups 0 and 1 also move dQ, dV and dK out of TMEM
+constexpr int kReaders = 256;  // D = 64: warpgroups 0 and 1 move dQ out of TMEM (D = 128: all four do)
 constexpr int kTmemCols = 512;
 constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-row tile
 
@@ -59,14 +60,16 @@ struct Cfg {
   // With D = 64 there is room (TMEM columns and shared memory) to overlap the
   // steps: two dQ accumulators, two dS^T tiles, two Q / dO stages, and dQ leaves
   // through a staging tile and TMA reductions.  With D = 128 the steps run one
-  // after the other and dQ is added with red.global.
+  // after the other.
   static constexpr bool kPipe = (D == 64);
   static constexpr int NQ = kPipe ? 2 : 1;         // Q / dO ring depth
   static constexpr int NDS = kPipe ? 2 : 1;        // dS^T tiles
   static constexpr int kDsBytes = BM * BQ * 2;     // one dS^T tile
-  static constexpr int kDqStage = kPipe ? 2 * BQ * 128 : 0;  // two boxes of 128 rows x 32 floats
+  // dQ staging: boxes of 128 rows x 32 floats, one per warpgroup that drains (two with D = 64, four with D = 128)
+  static constexpr int kDqStage = (kPipe ? 2 : 4) * BQ * 128;
   static constexpr int kVecBytes = 2 * 2 * BQ * 4; // lse / delta vectors, double buffered
-  static constexpr int kSmem = 2 * TB + 2 * NQ * TB + NDS * kDsBytes + kDqStage + kVecBytes + 1024 + 256;
+  static constexpr int kSmem = 2 * TB + 2 * NQ * TB + NDS * kDsBytes + kDqStage + kVecBytes + 256;
+  static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
 };
 
 // Developer aid, compiled out by default: with -DTT_ATTN_PROFILE the first CTA
@@ -105,14 +108,19 @@ __global__ void __launch_bounds__(kThreads, 1)
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   constexpr int TB = C::TB, NQ = C::NQ, HALVES = D / 64;
   constexpr bool kPipe = C::kPipe;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // 128-byte-swizzled tiles must start on a 1024-byte boundary; with D = 128 there is
+  // no room for alignment slack, so the array itself carries the requirement
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((ptx::smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && a.status) atomicOr(a.status, kStatusBadSmemAlign);
+    return;
+  }
   uint8_t* sK = smem;
   uint8_t* sV = sK + TB;
   uint8_t* sQ = sV + TB;          // NQ tiles
   uint8_t* sdO = sQ + NQ * TB;    // NQ tiles
   uint8_t* sdS = sdO + NQ * TB;   // NDS x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
-  uint8_t* sdq = sdS + C::NDS * C::kDsBytes;  // dQ staging (kPipe): per warpgroup [128 queries][32 floats], swizzled
+  uint8_t* sdq = sdS + C::NDS * C::kDsBytes;  // dQ staging: per draining warpgroup [128 queries][32 floats], swizzled
   float* svec = reinterpret_cast<float*>(sdq + C::kDqStage);  // [2 buffers][lse2 | delta][128]
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(reinterpret_cast<uint8_t*>(svec) + C::kVecBytes);
   volatile int* abort_flag = &ctl->abort_flag;
@@ -147,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&ctl->dq_full[i], 1);
-      ptx::mbar_init(&ctl->dq_free[i], kReaders);
+      ptx::mbar_init(&ctl->dq_free[i], kPipe ? kReaders : kCompute);
     }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -155,7 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tma_prefetch_desc(&tmK);
     ptx::tma_prefetch_desc(&tmV);
     ptx::tma_prefetch_desc(&tmdO);
-    if (kPipe) ptx::tma_prefetch_desc(&tmdQ);
+    ptx::tma_prefetch_desc(&tmdQ);
   }
   if (warp == 17) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -304,52 +312,33 @@ __global__ void __launch_bounds__(kThreads, 1)
       svec[r] = l0;
       svec[BQ + r] = d0;
     }
-    // dQ of step n -> global; thread r owns query row q0 + r, warpgroup w the
-    // columns [w*D/2, (w+1)*D/2)
+    // dQ of step n -> global; thread r owns query row q0 + r, warpgroup w the columns
+    // [32w, 32w+32) (D = 64: warpgroups 0 and 1; D = 128: all four): through a swizzled
+    // staging tile and one TMA reduction per warpgroup (coalesced; rows beyond Lq are
+    // clipped by the tensor map)
     auto read_out_dq = [&](int n) {
       const int h = hk * group + n / per_head;
       const int q0 = (qt_begin + n % per_head) * BQ;
       const int buf = kPipe ? (n & 1) : 0;
       if (ok) ok = ptx::mbar_wait(&ctl->dq_full[buf], (kPipe ? (n >> 1) : n) & 1, abort_flag);
       ptx::tc_fence_after();
-      if constexpr (kPipe) {
-        // through a swizzled staging tile and one TMA reduction per warpgroup
-        // (coalesced; rows beyond Lq are clipped by the tensor map)
-        uint32_t v[32];
-        ptx::tmem_ld32(tdQ(n) + lane_addr + wg * 32, v);
-        ptx::tmem_wait_ld();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(&ctl->dq_free[buf]);
-        uint8_t* stage = sdq + wg * (BQ * 128);
-        if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging tile
-        ptx::named_barrier(3 + wg, BM);
+      uint32_t v[32];
+      ptx::tmem_ld32(tdQ(n) + lane_addr + wg * 32, v);
+      ptx::tmem_wait_ld();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&ctl->dq_free[buf]);
+      uint8_t* stage = sdq + wg * (BQ * 128);
+      if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging tile
+      ptx::named_barrier(3 + wg, BM);
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch)
-          *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
-              make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
-        ptx::fence_proxy_async_smem();
-        ptx::named_barrier(3 + wg, BM);
-        if (r == 0 && ok) {
-          ptx::tma_reduce_add_4d(&tmdQ, stage, wg * 32, q0, h, b);
-          ptx::bulk_commit();
-        }
-      } else {
-        float* dq_row = a.dq_accum + ((static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q0 + r) * D + wg * (D / 2);
-#pragma unroll
-        for (int cc = 0; cc < D / 64; ++cc) {
-          uint32_t v[32];
-          ptx::tmem_ld32(tdQ(n) + lane_addr + wg * (D / 2) + cc * 32, v);
-          ptx::tmem_wait_ld();
-          if (ok && q0 + r < a.Lq) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              atomicAdd(reinterpret_cast<float4*>(dq_row + cc * 32 + i),
-                        make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                                    __uint_as_float(v[i + 3])));
-          }
-        }
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(&ctl->dq_free[0]);
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
+            make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+      ptx::fence_proxy_async_smem();
+      ptx::named_barrier(3 + wg, BM);
+      if (r == 0 && ok) {
+        ptx::tma_reduce_add_4d(&tmdQ, stage, wg * 32, q0, h, b);
+        ptx::bulk_commit();
       }
     };
 
@@ -439,19 +428,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         nv[BQ + r] = dn;
       }
       // dQ: of the previous step while this step's MMAs run (kPipe), else of this step
-      if (wg < 2) {
-        if (kPipe) {
-          if (n >= 1) read_out_dq(n - 1);
-        } else {
-          read_out_dq(n);
-        }
+      if (kPipe) {
+        if (wg < 2 && n >= 1) read_out_dq(n - 1);
+      } else {
+        read_out_dq(n);
       }
       TT_BSTAMP(wg, 6);
     }
-    if (kPipe && n_steps > 0 && wg < 2) {
-      read_out_dq(n_steps - 1);
-      if (r == 0) ptx::bulk_wait_all();
-    }
+    if (kPipe && n_steps > 0 && wg < 2) read_out_dq(n_steps - 1);
+    if (r == 0) ptx::bulk_wait_all();
 
     // dV (warpgroup 0) and dK (warpgroup 1) of this key tile
     T* out = nullptr;
