@@ -260,6 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
                        (n > 0 || ks > 0) ? 1u : 0u);
         }
+        if (!kPipe) ptx::mma_commit(&ctl->q_empty[st]);  // Q and dO of this step have been read (dV, dK above)
         if (kPipe) {
           // P^T / dS^T of this step have been consumed from TMEM (in issue order):
           // the next step's S^T / dP^T go first, then this step's dQ, which reads
@@ -272,11 +273,28 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ss2(tdQ(n), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
         }
         ptx::mma_commit(&ctl->dq_full[kPipe ? (n & 1) : 0]);
-        ptx::mma_commit(&ctl->q_empty[st]);
+        if (kPipe) ptx::mma_commit(&ctl->q_empty[st]);
         if (!kPipe && n + 1 < n_steps) {
-          // region A holds this step's dQ until the compute threads have read it
+          // (the single Q / dO stage was handed back after dK above, so its reload runs under
+          // the dQ MMAs and the read-out.)  dP^T of the next step can go into region B at once:
+          // dS^T there has been consumed in issue order.  Region A holds this step's dQ until the
+          // compute threads have read it: S^T of the next step waits for that.
+          if (!(ok = ptx::mbar_wait(&ctl->q_full[(n + 1) % NQ], ((n + 1) / NQ) & 1, abort_flag))) break;
+          ptx::tc_fence_after();
+          const uint32_t qlo = stage_lo(sQ, n + 1, 16), dolo = stage_lo(sdO, n + 1, 16);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+            ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          }
           if (!(ok = ptx::mbar_wait(&ctl->dq_free[0], n & 1, abort_flag))) break;
-          if (!(ok = issue_s_dp(n + 1))) break;
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+            ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          }
+          ptx::mma_commit(&ctl->sp_full);
         }
       }
       if (ok) ptx::mma_commit(&ctl->acc_full);
