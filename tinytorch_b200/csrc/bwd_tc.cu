@@ -48,7 +48,7 @@ constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-ro
 struct __align__(8) SmemCtl {
   uint64_t kv_full;
   uint64_t q_full[2], q_empty[2];
-  uint64_t sp_full, pds_full, acc_full;
+  uint64_t sp_full, pds_half, pds_full, acc_full;  // pds_half: the first 16 queries of every warpgroup are done
   uint64_t dq_full[2], dq_free[2];  // per dQ buffer
   uint32_t tmem_base;
   int abort_flag;
@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     ptx::mbar_init(&ctl->sp_full, 1);
     ptx::mbar_init(&ctl->pds_full, kCompute);
+    ptx::mbar_init(&ctl->pds_half, kCompute);
     ptx::mbar_init(&ctl->acc_full, 1);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -248,18 +249,23 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int st = n % NQ;
         const uint32_t qlo_mn = stage_lo(sQ, n, kHalfBytes), dolo_mn = stage_lo(sdO, n, kHalfBytes);
         const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (n % C::NDS) * C::kDsBytes), kHalfBytes);
-        if (!(ok = ptx::mbar_wait(&ctl->pds_full, n & 1, abort_flag))) break;
-        ptx::tc_fence_after();
+        // dV and dK contract over the 128 queries, 16 per k-step (2048 bytes of B).  Warpgroup w forms
+        // the queries of k-step 2w first and of k-step 2w+1 second, so the even k-steps run while the
+        // odd ones are still being computed.
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks) {  // contraction over the 128 queries, 16 per step = 2048 bytes of B
-          ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
-                       (n > 0 || ks > 0) ? 1u : 0u);
-        }
+        for (int half = 0; half < 2; ++half) {
+          if (!(ok = ptx::mbar_wait(half == 0 ? &ctl->pds_half : &ctl->pds_full, n & 1, abort_flag))) break;
+          ptx::tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks) {
-          ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
-                       (n > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = half; ks < BQ / 16; ks += 2)
+            ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+                         (n > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+          for (int ks = half; ks < BQ / 16; ks += 2)
+            ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+                         (n > 0 || ks > 0) ? 1u : 0u);
         }
+        if (!ok) break;
         if (!kPipe) ptx::mma_commit(&ctl->q_empty[st]);  // Q and dO of this step have been read (dV, dK above)
         if (kPipe) {
           // P^T / dS^T of this step have been consumed from TMEM (in issue order):
@@ -425,6 +431,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         // columns another warpgroup still has to read.
         ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
         ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
+        if (sc == 0) {
+          // P^T / dS^T of this warpgroup's first 16 queries are in TMEM: dV / dK may start on them
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(&ctl->pds_half);
+        }
         // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
         uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
 #pragma unroll
