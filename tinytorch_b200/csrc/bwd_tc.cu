@@ -317,24 +317,29 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
 
     // per-query vectors of step n live in svec[(n & 1)]: [0,128) -lse * log2(e), [128,256) -delta * scale;
-    // warpgroup 0 fetches them one step ahead
-    auto load_vec = [&](int n, float& lse2, float& dl) {
+    // warpgroup 0 fetches them one step ahead.  load_vec only issues the two loads (raw values: nothing
+    // may depend on them before the step's barrier, or the whole CTA would wait for their latency);
+    // store_vec converts and stores them a step's work later.
+    auto load_vec = [&](int n, float& lse, float& delta) {
       const int h = hk * group + n / per_head;
       const int q = (qt_begin + n % per_head) * BQ + r;
-      lse2 = -INFINITY;  // rows beyond Lq: P = 2^(x - inf) = 0
-      dl = 0.f;
+      lse = -INFINITY;  // rows beyond Lq behave like rows without any participating key: P = 0
+      delta = 0.f;
       if (q < a.Lq) {
         const int64_t idx = (static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q;
-        const float lse = a.lse[idx];
-        lse2 = lse == -INFINITY ? -INFINITY : -lse * kLog2e;  // a row without any participating key: P = 0
-        dl = -a.delta[idx] * a.scale;
+        lse = a.lse[idx];
+        delta = a.delta[idx];
       }
+    };
+    auto store_vec = [&](int n, float lse, float delta) {
+      float* nv = svec + (n & 1) * 2 * BQ;
+      nv[r] = lse == -INFINITY ? -INFINITY : -lse * kLog2e;
+      nv[BQ + r] = -delta * a.scale;
     };
     if (n_steps > 0 && wg == 0) {
       float l0, d0;
       load_vec(0, l0, d0);
-      svec[r] = l0;
-      svec[BQ + r] = d0;
+      store_vec(0, l0, d0);
     }
     // dQ of step n -> global; thread r owns query row q0 + r, warpgroup w the columns
     // [32w, 32w+32) (D = 64: warpgroups 0 and 1; D = 128: all four): through a swizzled
@@ -370,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int q0 = (qt_begin + n % per_head) * BQ;
       const float* vec = svec + (n & 1) * 2 * BQ;
       uint8_t* ds_tile = sdS + (n % C::NDS) * C::kDsBytes;
-      float ln = 0.f, dn = 0.f;
+      float ln = -INFINITY, dn = 0.f;
       if (wg == 0 && n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
       // all threads reach this point every step, expired waits included
       TT_BSTAMP(wg, 0);
@@ -452,11 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::tc_fence_before();
       ptx::mbar_arrive(&ctl->pds_full);
       TT_BSTAMP(wg, 4);
-      if (wg == 0 && n + 1 < n_steps) {
-        float* nv = svec + ((n + 1) & 1) * 2 * BQ;
-        nv[r] = ln;
-        nv[BQ + r] = dn;
-      }
+      if (wg == 0 && n + 1 < n_steps) store_vec(n + 1, ln, dn);
       // dQ: of the previous step while this step's MMAs run (kPipe), else of this step
       if (kPipe) {
         if (wg < 2 && n >= 1) read_out_dq(n - 1);
