@@ -57,6 +57,49 @@ def test_rows_beyond_length_are_ignored(oracle):
     assert torch.equal(o1, o2)
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("Hq,Hkv,cap,lens", [
+    (8, 4, 300, (300, 1, 129)),            # 2 heads per kv head, one split
+    (8, 2, 4096, (4096, 513, 2000)),       # 4 per kv head, several splits, one of them empty for the short sequence
+    (16, 2, 1000, (1000, 128, 999)),       # 8 per kv head
+    (32, 2, 640, (640, 5, 600)),           # 16 per kv head (the most one MMA column block holds)
+    (12, 4, 1536, (1536, 1024, 1)),        # 3 per kv head: rows of the Q tile beyond the group are zero
+])
+def test_grouped_query_decode_on_tensor_cores(oracle, dt, Hq, Hkv, cap, lens):
+    # several query heads per kv head, D = 128, 16-bit: the tcgen05 decode path; rows at or beyond the
+    # lengths hold NaN / Inf and must not reach the result
+    B, D = len(lens), 128
+    q, qn = make((B, Hq, 1, D), DTYPES[dt], 91)
+    k, kn = make((B, Hkv, cap, D), DTYPES[dt], 92)
+    v, vn = make((B, Hkv, cap, D), DTYPES[dt], 93)
+    ln = np.array(lens, dtype=np.int32)
+    for b in range(B):
+        k[b, :, int(ln[b]):] = float("nan")
+        v[b, :, int(ln[b]):] = float("inf")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    from tinytorch_b200 import op
+    o, lse = op.sdpAttentionDecode(q, k, v, torch.from_numpy(ln).cuda(), needLse=True)
+    torch.cuda.synchronize()
+    assert not bool(torch.isnan(o.float()).any())
+    wo, wl = oracle.fwd(qn, kn, vn, kv_lens=ln)
+    assert np.abs(to_np(o) - wo).max() <= TOL_ABS_16BIT
+    assert np.abs(to_np(lse) - wl[:, :, 0]).max() <= 2e-2
+
+
+def test_grouped_query_decode_agrees_with_the_scan_kernel(oracle):
+    # the same cache read as 4 query heads per kv head (tensor cores) and, head by head, as 1 per kv head (scan)
+    B, Hq, Hkv, cap, D = 3, 8, 2, 2500, 128
+    q, _ = make((B, Hq, 1, D), torch.bfloat16, 95)
+    k, _ = make((B, Hkv, cap, D), torch.bfloat16, 96)
+    v, _ = make((B, Hkv, cap, D), torch.bfloat16, 97)
+    lens = torch.tensor([2500, 700, 1], dtype=torch.int32, device="cuda")
+    o, _ = _decode(q, k, v, lens)
+    g = Hq // Hkv
+    for h in range(Hq):
+        oh, _ = _decode(q[:, h:h + 1].contiguous(), k[:, h // g:h // g + 1], v[:, h // g:h // g + 1], lens)
+        assert float((o[:, h:h + 1].float() - oh.float()).abs().max()) <= 1e-2
+
+
 def test_config4_full(oracle):
     # B=64 H=32 D=128 bf16, cache of 8192, lengths uniform in [1024, 8192]
     B, H, cap, D = 64, 32, 8192, 128

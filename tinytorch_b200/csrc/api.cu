@@ -132,7 +132,7 @@ size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int 
   if (kind == TT_ATTN_KIND_DECODE) {
     if (Skv <= 0) return 0;
     int nsplit, chunk;
-    decode_plan(Skv, &nsplit, &chunk);
+    decode_plan_for(dtype, D, B, Hq, Hkv, Skv, &nsplit, &chunk);
     if (nsplit == 1) return 0;
     return round256(static_cast<size_t>(B) * Hq * nsplit * (D + 2) * sizeof(float));
   }
@@ -240,7 +240,7 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
   a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.capacity = p->capacity;
   a.scale = p->scale;
   a.kv_lens = p->kv_lens;
-  decode_plan(p->capacity, &a.nsplit, &a.chunk);
+  decode_plan_for(p->dtype, p->D, p->B, p->Hq, p->Hkv, p->capacity, &a.nsplit, &a.chunk);
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;
@@ -248,6 +248,7 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
       tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
   a.partial = static_cast<float*>(ws.ptr);
+  a.status = p->status;
   cudaError_t e = launch_decode(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
@@ -283,7 +284,7 @@ int tt_attn_decode_append(const tt_attn_decode_append_params* p) {
   a.rope_cos = p->rope_cos, a.rope_sin = p->rope_sin;
   a.rope_positions = p->rope_positions, a.rope_interleaved = p->rope_interleaved;
   a.status = p->status;
-  decode_plan(p->capacity, &a.nsplit, &a.chunk);
+  decode_plan_for(p->dtype, p->D, p->B, p->Hq, p->Hkv, p->capacity, &a.nsplit, &a.chunk);
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;
@@ -313,7 +314,7 @@ int tt_attn_decode_static(const tt_attn_decode_params* p) {
   a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.capacity = p->capacity;
   a.scale = p->scale;
   a.kv_lens = p->kv_lens;
-  decode_plan(p->capacity, &a.nsplit, &a.chunk);
+  decode_plan_for(p->dtype, p->D, p->B, p->Hq, p->Hkv, p->capacity, &a.nsplit, &a.chunk);
   const size_t need =
       tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   if (need > TT_ATTN_STATIC_SCRATCH_BYTES) return TT_ATTN_ERR_TOO_LARGE;

@@ -105,6 +105,9 @@ cudaError_t launch_bwd_delta(int dtype, int D, const BwdArgs& a, cudaStream_t st
 // fp16 / bf16 backward on the tensor cores; needs a.delta and a.dq_accum
 cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream);
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
+// grouped-query decode on the tensor cores (decode_tc.cu): 16-bit tensors, D = 128, 2..16 query heads per kv head
+bool decode_tc_applies(int dtype, int D, const DecodeArgs& a);
+cudaError_t launch_decode_tc(int dtype, const DecodeArgs& a, cudaStream_t stream);
 // rotary embedding of q and the new key, append of the new key / value row, then the same scan
 cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
 
@@ -122,6 +125,8 @@ cudaError_t launch_linear_tc(int dtype, const void* x, const void* w, const void
 
 // Split planning for decode, shared by the launcher and the workspace query.
 void decode_plan(int capacity, int* nsplit, int* chunk);
+// ... for the tensor-core path (several query heads per kv head): longer chunks, see decode.cu
+void decode_plan_for(int dtype, int D, int B, int Hq, int Hkv, int capacity, int* nsplit, int* chunk);
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

@@ -360,7 +360,37 @@ cudaError_t launch_d(int dtype, int D, const DecodeArgs& a, cudaStream_t stream)
   return D == 64 ? launch_t<__nv_bfloat16, 64, APPEND>(a, stream) : launch_t<__nv_bfloat16, 128, APPEND>(a, stream);
 }
 
+template <typename T, int D>
+cudaError_t combine_t(const DecodeArgs& a, cudaStream_t stream) {
+  decode_combine_kernel<T, D><<<dim3(a.Hq, a.B), D, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// The plan a call with these sizes uses (the launcher, the workspace query and the entry points agree
+// through this one function).  The tensor-core path pays a few thousand cycles at every item boundary
+// (the two softmax chains are merged there), so its chunks are 2048 rows - 16 tiles - unless that would
+// leave fewer than about two items per SM.
+void decode_plan_for(int dtype, int D, int B, int Hq, int Hkv, int capacity, int* nsplit, int* chunk) {
+  DecodeArgs probe{};
+  probe.Hq = Hq, probe.Hkv = Hkv;
+  if (!decode_tc_applies(dtype, D, probe)) {
+    decode_plan(capacity, nsplit, chunk);
+    return;
+  }
+  int ck = 2048;
+  while (ck > 512 && static_cast<long long>(B) * Hkv * ((capacity + ck - 1) / ck) < 296) ck >>= 1;
+  if ((capacity + ck - 1) / ck > 64) ck = (((capacity + 63) / 64) + 127) / 128 * 128;
+  *chunk = ck;
+  *nsplit = capacity <= ck ? 1 : (capacity + ck - 1) / ck;
+}
+
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
+  if (decode_tc_applies(dtype, D, a)) {
+    // several query heads per kv head: the tensor-core scan, then the same combine kernel
+    cudaError_t e = launch_decode_tc(dtype, a, stream);
+    if (e != cudaSuccess || a.nsplit == 1) return e;
+    return dtype == TT_ATTN_F16 ? combine_t<__half, 128>(a, stream) : combine_t<__nv_bfloat16, 128>(a, stream);
+  }
   return launch_d<false>(dtype, D, a, stream);
 }
 
