@@ -266,9 +266,11 @@ TT_ATTN_API int tt_attn_decode_append(const tt_attn_decode_append_params* p);
  *  - The first call on each device looks up the array's device address (once,
  *    with that device current); make that first call before starting any stream
  *    capture.
- *  - All calls on a device share the one array, which is never cleared (no part
- *    of it needs to start at zero); calls that overlap in time on the same GPU
- *    race on it, so keep them on one stream or otherwise ordered.
+ *  - All calls on a device share the one array; calls that overlap in time on the
+ *    same GPU race on it, so keep them on one stream or otherwise ordered.  It is
+ *    never cleared as a whole: every launch writes what it later reads, and the one
+ *    4-byte work counter that grouped-query shapes use is reset by a memset enqueued
+ *    on the call's stream.
  * This entry point has no counterpart in the reference. */
 #define TT_ATTN_STATIC_SCRATCH_BYTES (24u << 20)
 TT_ATTN_API int tt_attn_decode_static(const tt_attn_decode_params* p);

@@ -100,6 +100,12 @@ def test_workspace_sizes(lib):
     # decode: 512-row chunks -> 16 splits at capacity 8192; (D + 2) floats per (b, h, split)
     assert w(_capi.KIND_DECODE, 2, 64, 32, 32, 1, 8192, 128) == 64 * 32 * 16 * 130 * 4
     assert w(_capi.KIND_DECODE, 2, 64, 32, 32, 1, 512, 128) == 0
+    # several query heads per kv head (16-bit, D = 128): the tensor-core path plans 2048-row chunks when there are
+    # enough items to fill the GPU, and needs a 256-byte work counter besides the partials
+    assert w(_capi.KIND_DECODE, 2, 64, 32, 8, 1, 8192, 128) == 64 * 32 * 4 * 130 * 4 + 256
+    assert w(_capi.KIND_DECODE, 2, 64, 32, 8, 1, 1024, 128) == 256
+    assert w(_capi.KIND_DECODE, 2, 1, 32, 8, 1, 8192, 128) == 1 * 32 * 16 * 130 * 4 + 256   # few items: 512-row chunks
+    assert w(_capi.KIND_DECODE, 0, 64, 32, 8, 1, 8192, 128) == 64 * 32 * 16 * 130 * 4       # fp32 stays on the scan kernel
 
 
 def test_ops_refuse_cpu_tensors():

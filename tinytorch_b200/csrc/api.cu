@@ -133,8 +133,12 @@ size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int 
     if (Skv <= 0) return 0;
     int nsplit, chunk;
     decode_plan_for(dtype, D, B, Hq, Hkv, Skv, &nsplit, &chunk);
-    if (nsplit == 1) return 0;
-    return round256(static_cast<size_t>(B) * Hq * nsplit * (D + 2) * sizeof(float));
+    // per-split partials, and for the tensor-core path (several query heads per kv head) a work counter
+    DecodeArgs probe{};
+    probe.Hq = Hq, probe.Hkv = Hkv;
+    const size_t counter = decode_tc_applies(dtype, D, probe) ? 256 : 0;
+    if (nsplit == 1) return counter;
+    return round256(static_cast<size_t>(B) * Hq * nsplit * (D + 2) * sizeof(float)) + counter;
   }
   return 0;
 }
@@ -248,6 +252,7 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
       tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
   a.partial = static_cast<float*>(ws.ptr);
+  a.sched = need >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + need - 256) : nullptr;
   a.status = p->status;
   cudaError_t e = launch_decode(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);

@@ -94,6 +94,7 @@ struct DecodeArgs {
   int rope_interleaved;            // pairs (2i, 2i+1) instead of (i, i + D/2)
   int32_t* new_lens;               // optional [B]: kv_lens[b] + 1
   int32_t* status;
+  int* sched;                      // tensor-core path: work counter in scratch memory, zeroed by the launcher
 };
 
 // Each returns a cudaError_t from the launch (no synchronisation).

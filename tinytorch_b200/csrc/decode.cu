@@ -409,9 +409,11 @@ cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStre
 // until the process exits, hence the modest size.
 //
 // The array is shared by every call on a device and keeps the previous call's
-// contents.  Nothing in it has to start at zero: each launch writes every
-// (batch, head, split) slot before the combine kernel reads it.  Two calls that
-// overlap on the GPU (different streams) would race on it.
+// contents.  Each launch writes every (batch, head, split) slot before the combine
+// kernel reads it; the only word that must start at zero, the tensor-core path's
+// work counter in the last 256 bytes of what a call uses, is reset by a memset on
+// the call's stream.  Two calls that overlap on the GPU (different streams) would
+// race on the array.
 namespace {
 
 constexpr size_t kStaticScratchBytes = TT_ATTN_STATIC_SCRATCH_BYTES;
@@ -442,6 +444,7 @@ cudaError_t launch_decode_static(int dtype, int D, DecodeArgs a, size_t need, in
     ptr = g_scratch_ptr[device];
   }
   a.partial = static_cast<float*>(ptr);
+  a.sched = need >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ptr) + need - 256) : nullptr;
   return launch_decode(dtype, D, a, stream);
 }
 

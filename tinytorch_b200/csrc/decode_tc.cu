@@ -10,7 +10,8 @@
 //                                        (A = the V tile read MN-major, B = P K-major)
 // Q of the group (rows beyond G are zero) is staged in shared memory one work item ahead.
 //
-// One CTA per SM walks work items (batch, kv head, split) in a fixed order:
+// One CTA per SM draws work items (batch, kv head, split) from a global counter (sequences differ in
+// length, and a fixed assignment left SMs idle at the end: 3.9 against 6.2 TB/s):
 //   warp 0      producer: publishes the items that have keys through a small FIFO (one
 //               item ahead of its loads), writes the empty result of items without keys
 //               itself, and streams K / V tiles of 128 keys through a 3-stage TMA ring
@@ -161,11 +162,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     // lane 0 publishes the others and issues the loads.
     uint32_t g = 0, pub = 0;
     bool ok = true;
-    // publishes the next item with keys at or after w (or the end marker); returns its index
-    auto publish_next = [&](int w, ItemDesc* out) {
+    // draws items from the counter until one has keys, publishes it (or the end marker)
+    auto publish_next = [&](ItemDesc* out) {
       ItemDesc it;
       it.n_tiles = -1;
-      for (; w < n_items; w += gridDim.x) {
+      for (;;) {
+        int w = 0;
+        if (lane == 0) w = atomicAdd(a.sched, 1);
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (w >= n_items) break;
         it = item_of(a, w);
         if (it.n_tiles > 0) break;
         for (int h = 0; h < group; ++h) {
@@ -189,13 +194,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ++pub;
       *out = it;
-      return w;
     };
     ItemDesc cur;
-    int w = publish_next(blockIdx.x, &cur);
+    publish_next(&cur);
     while (cur.n_tiles > 0) {
       ItemDesc nxt;
-      const int wn = publish_next(w + gridDim.x, &nxt);  // one item ahead of the loads
+      publish_next(&nxt);  // one item ahead of the loads
       if (lane == 0) {
         for (int j = 0; j < cur.n_tiles && ok; ++j, ++g) {
           const int s = g % NSTAGE;
@@ -213,7 +217,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       cur = nxt;
-      w = wn;
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- issuer --
@@ -520,7 +523,9 @@ cudaError_t launch_t(int dtype, const DecodeArgs& a, cudaStream_t stream) {
   e = cudaGetDevice(&device);
   if (e != cudaSuccess) return e;
   const long long n_items = static_cast<long long>(a.B) * a.Hkv * a.nsplit;
-  if (n_items > 0x7fffffffll) return cudaErrorInvalidValue;
+  if (n_items > 0x7fffffffll || !a.sched) return cudaErrorInvalidValue;
+  e = cudaMemsetAsync(a.sched, 0, sizeof(int), stream);  // the work counter starts at zero for every launch
+  if (e != cudaSuccess) return e;
   const int sms = sm_count(device);
   kern<<<static_cast<unsigned>(n_items < sms ? n_items : sms), kThreads, kSmem, stream>>>(tk, tv, a, static_cast<int>(n_items));
   return cudaGetLastError();
