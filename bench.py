@@ -53,6 +53,10 @@ WORKLOADS = {
     # the QKV projection in front of attention: 16384 tokens, hidden 4096 -> 3 x 4096 (tensor bound)
     "linear": dict(kind="fused", opname="linear", dtype="bf16", rows=16384, dim=4096, n_out=12288),
     "linear_ncu": dict(kind="fused", opname="linear", dtype="bf16", rows=4096, dim=4096, n_out=4096),
+    # grouped-query decode (4 query heads per kv head): the tensor-core decode kernel
+    "decode_gqa": dict(kind="decode", dtype="bf16", B=256, Hq=32, Hkv=8, L=1, S=8192, D=128, causal=False, std=1.0),
+    "decode_gqa_ncu": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=8, L=1, S=8192, D=128, causal=False, std=1.0),
+    "train128_ncu": dict(kind="fwdbwd", dtype="bf16", B=1, Hq=16, Hkv=16, L=4096, S=4096, D=128, causal=True, std=1.0),
     "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
@@ -332,7 +336,7 @@ def run_ours(args, w, wname):
         res["roofline"] = {"bound": "hbm" if decode else "tensor", "achieved": per_gpu, "peak": peak,
                            "unit": "GB/s" if decode else "TFLOP/s", "frac": per_gpu / peak, "traffic": None,
                            "peak_source": peaks["source"],
-                           "kernel": "decode_kernel" if decode else ("fwd_simt_kernel" if wl["dtype"] == "f32" else "fwd_tc_kernel")}
+                           "kernel": ("decode_tc_kernel" if wl["Hq"] != wl["Hkv"] else "decode_kernel") if decode else ("fwd_simt_kernel" if wl["dtype"] == "f32" else "fwd_tc_kernel")}
         if with_e2e:
             # public API with HOST buffers: pinned inputs -> device, op, result -> pinned host, every step
             hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
