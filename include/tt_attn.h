@@ -239,13 +239,19 @@ typedef struct tt_attn_decode_append_params {
   int32_t rope_interleaved;
   int32_t device;
   void* stream;
-  void* workspace; /* as tt_attn_decode: tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, ...) */
+  void* workspace; /* tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE_APPEND, ...) */
   size_t workspace_bytes;
   const tt_attn_alloc_hook* alloc;
   int32_t* status;
 } tt_attn_decode_append_params;
 
-enum tt_attn_kind { TT_ATTN_KIND_FWD = 0, TT_ATTN_KIND_BWD = 1, TT_ATTN_KIND_DECODE = 2 };
+enum tt_attn_kind {
+  TT_ATTN_KIND_FWD = 0,
+  TT_ATTN_KIND_BWD = 1,
+  TT_ATTN_KIND_DECODE = 2,
+  TT_ATTN_KIND_DECODE_APPEND = 3 /* tt_attn_decode_append: the decode scratch, plus a rotated copy of q and the
+                                    new lengths when the grouped-query tensor-core path is taken */
+};
 
 TT_ATTN_API int tt_attn_fwd(const tt_attn_fwd_params* p);
 TT_ATTN_API int tt_attn_bwd(const tt_attn_bwd_params* p);

@@ -106,6 +106,10 @@ def test_workspace_sizes(lib):
     assert w(_capi.KIND_DECODE, 2, 64, 32, 8, 1, 1024, 128) == 256
     assert w(_capi.KIND_DECODE, 2, 1, 32, 8, 1, 8192, 128) == 1 * 32 * 16 * 130 * 4 + 256   # few items: 512-row chunks
     assert w(_capi.KIND_DECODE, 0, 64, 32, 8, 1, 8192, 128) == 64 * 32 * 16 * 130 * 4       # fp32 stays on the scan kernel
+    # the fused decode step: same scratch, plus the rotated q and the new lengths on the tensor-core path
+    assert w(_capi.KIND_DECODE_APPEND, 2, 64, 32, 32, 1, 8192, 128) == w(_capi.KIND_DECODE, 2, 64, 32, 32, 1, 8192, 128)
+    assert w(_capi.KIND_DECODE_APPEND, 2, 64, 32, 8, 1, 8192, 128) == \
+        w(_capi.KIND_DECODE, 2, 64, 32, 8, 1, 8192, 128) + 64 * 32 * 128 * 2 + 256
 
 
 def test_ops_refuse_cpu_tensors():

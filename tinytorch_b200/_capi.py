@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TT_ATTN_LIB") or os.path.join(HERE, "lib", "libtt_attn.so")
 
 F32, F16, BF16 = 0, 1, 2
-KIND_FWD, KIND_BWD, KIND_DECODE = 0, 1, 2
+KIND_FWD, KIND_BWD, KIND_DECODE, KIND_DECODE_APPEND = 0, 1, 2, 3
 CAUSAL_NONE, CAUSAL_TOP_LEFT, CAUSAL_BOTTOM_RIGHT = 0, 1, 2
 MASK_NONE, MASK_BOOL, MASK_ADD, MASK_ADD_F32 = 0, 1, 2, 3
 

@@ -129,6 +129,14 @@ size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int 
     const size_t rows = static_cast<size_t>(B) * Hq * (Lq > 0 ? Lq : 0);
     return round256(rows * sizeof(float)) + (dtype == TT_ATTN_F32 ? 0 : round256(rows * D * sizeof(float)));
   }
+  if (kind == TT_ATTN_KIND_DECODE_APPEND) {
+    // the decode scratch; on the grouped-query tensor-core path also the rotated q and the new lengths
+    const size_t base = tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, dtype, B, Hq, Hkv, Lq, Skv, D);
+    DecodeArgs probe{};
+    probe.Hq = Hq, probe.Hkv = Hkv;
+    if (Skv <= 0 || !decode_tc_applies(dtype, D, probe)) return base;
+    return base + round256(static_cast<size_t>(B) * Hq * D * elem_size(dtype)) + round256(static_cast<size_t>(B) * 4);
+  }
   if (kind == TT_ATTN_KIND_DECODE) {
     if (Skv <= 0) return 0;
     int nsplit, chunk;
@@ -248,10 +256,17 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;
-  const size_t need =
+  const size_t base =
       tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
+  const size_t need =
+      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE_APPEND, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
   a.partial = static_cast<float*>(ws.ptr);
+  a.sched = base >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + base - 256) : nullptr;
+  if (need > base) {
+    a.q_rot = static_cast<char*>(ws.ptr) + base;
+    a.lens_scratch = reinterpret_cast<int32_t*>(static_cast<char*>(ws.ptr) + need - round256(static_cast<size_t>(p->B) * 4));
+  }
   a.sched = need >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + need - 256) : nullptr;
   a.status = p->status;
   cudaError_t e = launch_decode(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
@@ -293,10 +308,17 @@ int tt_attn_decode_append(const tt_attn_decode_append_params* p) {
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;
-  const size_t need =
+  const size_t base =
       tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
+  const size_t need =
+      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE_APPEND, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
   a.partial = static_cast<float*>(ws.ptr);
+  a.sched = base >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + base - 256) : nullptr;
+  if (need > base) {
+    a.q_rot = static_cast<char*>(ws.ptr) + base;
+    a.lens_scratch = reinterpret_cast<int32_t*>(static_cast<char*>(ws.ptr) + need - round256(static_cast<size_t>(p->B) * 4));
+  }
   cudaError_t e = launch_decode_append(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }

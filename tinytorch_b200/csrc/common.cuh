@@ -95,6 +95,8 @@ struct DecodeArgs {
   int32_t* new_lens;               // optional [B]: kv_lens[b] + 1
   int32_t* status;
   int* sched;                      // tensor-core path: work counter in scratch memory, zeroed by the launcher
+  void* q_rot;                     // append on the tensor-core path: scratch [B, Hq, D] for the rotated q
+  int32_t* lens_scratch;           // ... and [B] for the lengths after the append
 };
 
 // Each returns a cudaError_t from the launch (no synchronisation).

@@ -394,7 +394,68 @@ cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t st
   return launch_d<false>(dtype, D, a, stream);
 }
 
+namespace {
+
+// Grouped-query append on the tensor-core path, step 1: one CTA per (head, batch) rotates q into scratch
+// (heads 0..Hq-1) or rotates the new key and writes it and the new value into the caches (heads Hq..Hq+Hkv-1);
+// thread t handles the pair (t, t + D/2), or (2t, 2t+1) when interleaved.  The lengths after the append go to
+// lens_out.  Step 2 is the ordinary tensor-core decode over q_rot and lens_out.
+template <typename T, int D>
+__global__ void __launch_bounds__(D / 2) rope_append_kernel(const DecodeArgs a, int32_t* lens_out) {
+  const int hh = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+  int pos = a.kv_lens[b];
+  pos = pos < 0 ? 0 : pos;
+  const bool room = pos < a.capacity;
+  const bool rotate = a.rope_cos != nullptr && pos < a.rope_positions;
+  if (hh == 0 && t == 0) {
+    const int len = room ? pos + 1 : a.capacity;
+    lens_out[b] = len;
+    if (a.new_lens) a.new_lens[b] = len;
+    if (a.status && !room) atomicOr(a.status, kStatusCacheFull);
+    if (a.status && a.rope_cos != nullptr && !rotate) atomicOr(a.status, kStatusRopeRange);
+  }
+  const bool is_q = hh < a.Hq;
+  const int hk = hh - a.Hq;
+  if (!is_q && !room) return;  // nothing is appended to a full cache
+  const T* src = is_q ? reinterpret_cast<const T*>(a.q) + b * a.qs.b + hh * a.qs.h
+                      : reinterpret_cast<const T*>(a.k_new) + b * a.kn_b + hk * a.kn_h;
+  T* dst = is_q ? reinterpret_cast<T*>(a.q_rot) + (static_cast<int64_t>(b) * a.Hq + hh) * D
+                : const_cast<T*>(reinterpret_cast<const T*>(a.k)) + b * a.ks.b + hk * a.ks.h + static_cast<int64_t>(pos) * a.ks.s;
+  const int i0 = a.rope_interleaved ? 2 * t : t, i1 = a.rope_interleaved ? 2 * t + 1 : t + D / 2;
+  float x0 = to_f32<T>(src[i0]), x1 = to_f32<T>(src[i1]);
+  if (rotate) {
+    const float c = a.rope_cos[static_cast<int64_t>(pos) * (D / 2) + t], s = a.rope_sin[static_cast<int64_t>(pos) * (D / 2) + t];
+    const float y0 = x0 * c - x1 * s, y1 = x1 * c + x0 * s;
+    x0 = y0, x1 = y1;
+  }
+  dst[i0] = from_f32<T>(x0);
+  dst[i1] = from_f32<T>(x1);
+  if (!is_q) {
+    const T* vs = reinterpret_cast<const T*>(a.v_new) + b * a.vn_b + hk * a.vn_h;
+    T* vd = const_cast<T*>(reinterpret_cast<const T*>(a.v)) + b * a.vs.b + hk * a.vs.h + static_cast<int64_t>(pos) * a.vs.s;
+    vd[i0] = vs[i0];
+    vd[i1] = vs[i1];
+  }
+}
+
+template <typename T>
+cudaError_t append_tc_t(int dtype, const DecodeArgs& a, cudaStream_t stream) {
+  rope_append_kernel<T, 128><<<dim3(a.Hq + a.Hkv, a.B), 64, 0, stream>>>(a, a.lens_scratch);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  DecodeArgs d = a;
+  d.q = a.q_rot;
+  d.qs = Str3{static_cast<int64_t>(a.Hq) * 128, 128, 128};
+  d.kv_lens = a.lens_scratch;
+  return launch_decode(dtype, 128, d, stream);
+}
+
+}  // namespace
+
 cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
+  // several query heads per kv head: rotate / append in a small kernel, then the tensor-core decode
+  if (decode_tc_applies(dtype, D, a) && a.q_rot && a.lens_scratch)
+    return dtype == TT_ATTN_F16 ? append_tc_t<__half>(dtype, a, stream) : append_tc_t<__nv_bfloat16>(dtype, a, stream);
   return launch_d<true>(dtype, D, a, stream);
 }
 
