@@ -108,9 +108,9 @@ cudaError_t launch_bwd_delta(int dtype, int D, const BwdArgs& a, cudaStream_t st
 // fp16 / bf16 backward on the tensor cores; needs a.delta and a.dq_accum
 cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream);
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
-// grouped-query decode on the tensor cores (decode_tc.cu): 16-bit tensors, D = 128, 2..16 query heads per kv head
+// grouped-query decode on the tensor cores (decode_tc.cu): 16-bit tensors, 2..16 query heads per kv head
 bool decode_tc_applies(int dtype, int D, const DecodeArgs& a);
-cudaError_t launch_decode_tc(int dtype, const DecodeArgs& a, cudaStream_t stream);
+cudaError_t launch_decode_tc(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
 // rotary embedding of q and the new key, append of the new key / value row, then the same scan
 cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStream_t stream);
 

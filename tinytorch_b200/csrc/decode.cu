@@ -387,9 +387,10 @@ void decode_plan_for(int dtype, int D, int B, int Hq, int Hkv, int capacity, int
 cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
   if (decode_tc_applies(dtype, D, a)) {
     // several query heads per kv head: the tensor-core scan, then the same combine kernel
-    cudaError_t e = launch_decode_tc(dtype, a, stream);
+    cudaError_t e = launch_decode_tc(dtype, D, a, stream);
     if (e != cudaSuccess || a.nsplit == 1) return e;
-    return dtype == TT_ATTN_F16 ? combine_t<__half, 128>(a, stream) : combine_t<__nv_bfloat16, 128>(a, stream);
+    if (D == 128) return dtype == TT_ATTN_F16 ? combine_t<__half, 128>(a, stream) : combine_t<__nv_bfloat16, 128>(a, stream);
+    return dtype == TT_ATTN_F16 ? combine_t<__half, 64>(a, stream) : combine_t<__nv_bfloat16, 64>(a, stream);
   }
   return launch_d<false>(dtype, D, a, stream);
 }
@@ -438,24 +439,27 @@ __global__ void __launch_bounds__(D / 2) rope_append_kernel(const DecodeArgs a, 
   }
 }
 
-template <typename T>
+template <typename T, int D>
 cudaError_t append_tc_t(int dtype, const DecodeArgs& a, cudaStream_t stream) {
-  rope_append_kernel<T, 128><<<dim3(a.Hq + a.Hkv, a.B), 64, 0, stream>>>(a, a.lens_scratch);
+  rope_append_kernel<T, D><<<dim3(a.Hq + a.Hkv, a.B), D / 2, 0, stream>>>(a, a.lens_scratch);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   DecodeArgs d = a;
   d.q = a.q_rot;
-  d.qs = Str3{static_cast<int64_t>(a.Hq) * 128, 128, 128};
+  d.qs = Str3{static_cast<int64_t>(a.Hq) * D, D, D};
   d.kv_lens = a.lens_scratch;
-  return launch_decode(dtype, 128, d, stream);
+  return launch_decode(dtype, D, d, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_decode_append(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
   // several query heads per kv head: rotate / append in a small kernel, then the tensor-core decode
-  if (decode_tc_applies(dtype, D, a) && a.q_rot && a.lens_scratch)
-    return dtype == TT_ATTN_F16 ? append_tc_t<__half>(dtype, a, stream) : append_tc_t<__nv_bfloat16>(dtype, a, stream);
+  if (decode_tc_applies(dtype, D, a) && a.q_rot && a.lens_scratch) {
+    if (D == 128)
+      return dtype == TT_ATTN_F16 ? append_tc_t<__half, 128>(dtype, a, stream) : append_tc_t<__nv_bfloat16, 128>(dtype, a, stream);
+    return dtype == TT_ATTN_F16 ? append_tc_t<__half, 64>(dtype, a, stream) : append_tc_t<__nv_bfloat16, 64>(dtype, a, stream);
+  }
   return launch_d<true>(dtype, D, a, stream);
 }
 

@@ -35,13 +35,19 @@
 namespace ttattn {
 namespace {
 
-constexpr int D = 128, BK = 128, GP = 16, NSTAGE = 3, NFIFO = 4;
+constexpr int BK = 128, GP = 16, NFIFO = 4;
 constexpr int kThreads = 384, kSoft = 128;
-constexpr int kTile = BK * D * 2;          // one K or V tile
 constexpr int kHalf = BK * 128;            // one 64-column half of a tile
-constexpr int kStage = 2 * kTile;          // K + V
-constexpr int kQBytes = 2 * GP * 128;      // [16 heads][128 channels], two 64-channel blocks (x 2 buffers)
+constexpr int kQBytes = 2 * GP * 128;      // [16 heads][up to 128 channels], 64-channel blocks (x 2 buffers)
 constexpr int kPBytes = 2 * GP * 128;      // [16 heads][128 keys], two 64-key blocks (x 2 buffers)
+constexpr int kMaxStages = 6;
+// D = 128: 3 stages of 64 KB; D = 64: 6 stages of 32 KB (the same bytes in flight)
+template <int D>
+struct Cfg {
+  static constexpr int kTile = BK * D * 2;  // one K or V tile
+  static constexpr int kStage = 2 * kTile;  // K + V
+  static constexpr int NSTAGE = D == 128 ? 3 : 6;
+};
 constexpr int kTmemCols = 64;              // S^T x 2 and O^T x 2, 16 columns each
 constexpr int kItemConsumers = 1 + 2 * kSoft;  // issuer thread + both softmax warpgroups
 
@@ -50,7 +56,7 @@ struct ItemDesc {
 };
 
 struct __align__(8) SmemCtl {
-  uint64_t full[NSTAGE], empty[NSTAGE];
+  uint64_t full[kMaxStages], empty[kMaxStages];
   uint64_t item_full[NFIFO], item_empty[NFIFO];
   uint64_t q_full[2], q_empty[2], s_full[2], s_free[2], p_full[2], pv_done[2];
   uint64_t b_done, o_free;
@@ -61,7 +67,7 @@ struct __align__(8) SmemCtl {
   int abort_flag;
 };
 
-constexpr int kSmem = NSTAGE * kStage + 2 * kQBytes + 2 * kPBytes + static_cast<int>(sizeof(SmemCtl));
+constexpr int kSmem = 3 * 2 * BK * 128 * 2 + 2 * kQBytes + 2 * kPBytes + static_cast<int>(sizeof(SmemCtl));
 static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
 
 template <bool BF16>
@@ -102,11 +108,12 @@ __device__ __forceinline__ ItemDesc item_of(const DecodeArgs& a, int w) {
   return it;
 }
 
-template <bool BF16>
+template <bool BF16, int D>
 __global__ void __launch_bounds__(kThreads, 1)
     decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const DecodeArgs a,
                      int n_items) {
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  constexpr int kTile = Cfg<D>::kTile, kStage = Cfg<D>::kStage, NSTAGE = Cfg<D>::NSTAGE;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((ptx::smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0 && a.status) atomicOr(a.status, kStatusBadSmemAlign);
@@ -208,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mbar_arrive_expect_tx(&ctl->full[s], kStage);
           const int row = cur.begin + j * BK;  // rows beyond the cache read as zero
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
+          for (int hf = 0; hf < D / 64; ++hf) {
             ptx::tma_load_4d(st + hf * kHalf, &tmK, &ctl->full[s], hf * 64, row, cur.hk, cur.b);
             ptx::tma_load_4d(st + kTile + hf * kHalf, &tmV, &ctl->full[s], hf * 64, row, cur.hk, cur.b);
           }
@@ -224,7 +231,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
       const uint32_t fmt = BF16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc_f16(BK, GP, fmt, 0, 0);  // S^T: A = K tile, B = Q, both K-major
-      const uint32_t idesc_o = ptx::make_idesc_f16(D, GP, fmt, 1, 0);   // O^T: A = V tile MN-major, B = P K-major
+      // O^T: A = V tile MN-major (M = 128 channels; with D = 64 the second 64-channel block of the descriptor is the
+      // first one again, so lanes 64-127 of O^T repeat lanes 0-63 and are ignored), B = P K-major
+      const uint32_t idesc_o = ptx::make_idesc_f16(128, GP, fmt, 1, 0);
       uint32_t items = 0, tiles = 0;  // items / tiles so far (ring position = tiles)
       bool ok = true;
       // S^T = K_tile Q^T of global tile t (stage t % NSTAGE) into S^T buffer t & 1
@@ -266,7 +275,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!(ok = ptx::mbar_wait(&ctl->p_full[wb], (tiles >> 1) & 1, abort_flag))) break;
           ptx::tc_fence_after();
           const int s = tiles % NSTAGE;
-          const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(smem + s * kStage + kTile), kHalf);
+          const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(smem + s * kStage + kTile), D == 128 ? kHalf : 0);
           const uint32_t plo = ptx::smem_desc_lo(ptx::smem_u32(sP + wb * kPBytes), 16);
 #pragma unroll
           for (int ks = 0; ks < BK / 16; ++ks) {  // 16 keys per step: 2048 bytes of the V tile, 32 bytes of a P row
@@ -299,11 +308,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::mbar_arrive(&ctl->item_empty[slot]);
       return it;
     };
-    // Q of a group: 16 rows x 16 chunks of 16 bytes, two chunks per thread (rows beyond the group are zero)
+    // Q of a group: 16 rows x D/8 chunks of 16 bytes, D/64 chunks per thread (rows beyond the group are zero)
+    constexpr int CPR = D / 8;  // chunks per row
     auto load_q = [&](const ItemDesc& it, uint4 (&qv)[2]) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int idx = r + i * kSoft, n = idx >> 4, ch = idx & 15;
+      for (int i = 0; i < D / 64; ++i) {
+        const int idx = r + i * kSoft, n = idx / CPR, ch = idx % CPR;
         qv[i] = make_uint4(0, 0, 0, 0);
         if (n < group)
           qv[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + it.b * a.qs.b +
@@ -313,8 +323,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ... into shared-memory buffer qb (K-major, 128-byte swizzle), then signalled to the issuer
     auto store_q = [&](uint32_t qb, const uint4 (&qv)[2]) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int idx = r + i * kSoft, n = idx >> 4, ch = idx & 15;
+      for (int i = 0; i < D / 64; ++i) {
+        const int idx = r + i * kSoft, n = idx / CPR, ch = idx % CPR;
         *reinterpret_cast<uint4*>(sQ + qb * kQBytes + (ch >> 3) * (GP * 128) + n * 128 + (((ch & 7) ^ (n & 7)) << 4)) = qv[i];
       }
       ptx::fence_proxy_async_smem();
@@ -391,7 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!valid) {
           uint8_t* vt = smem + (t % NSTAGE) * kStage + kTile;
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf)
+          for (int hf = 0; hf < D / 64; ++hf)
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch)
               *reinterpret_cast<uint4*>(vt + hf * kHalf + r * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
@@ -483,15 +493,17 @@ __global__ void __launch_bounds__(kThreads, 1)
             float oh = (wa > 0.f ? __uint_as_float(oa[h]) * wa : 0.f) + (wb > 0.f ? __uint_as_float(ob[h]) * wb : 0.f);
             if (!ok) oh = 0.f;
             const int hq = h0 + h;
-            if (a.nsplit == 1) {
-              const float inv = lt > 0.f ? 1.f / lt : 0.f;
-              reinterpret_cast<T*>(a.o)[it.b * a.os.b + hq * a.os.h + r] = from_f32<T>(oh * inv);
-              if (a.lse && r == 0)
-                a.lse[static_cast<int64_t>(it.b) * a.Hq + hq] = lt > 0.f ? (mn + log2f(lt)) * kLn2 : -INFINITY;
-            } else {
-              float* pp = a.partial + ((static_cast<int64_t>(it.b) * a.Hq + hq) * a.nsplit + it.split) * (D + 2);
-              pp[r] = oh;
-              if (r == 0) pp[D] = lt > 0.f ? mn : -INFINITY, pp[D + 1] = lt;
+            if (r < D) {  // D = 64: lanes 64-127 hold copies
+              if (a.nsplit == 1) {
+                const float inv = lt > 0.f ? 1.f / lt : 0.f;
+                reinterpret_cast<T*>(a.o)[it.b * a.os.b + hq * a.os.h + r] = from_f32<T>(oh * inv);
+                if (a.lse && r == 0)
+                  a.lse[static_cast<int64_t>(it.b) * a.Hq + hq] = lt > 0.f ? (mn + log2f(lt)) * kLn2 : -INFINITY;
+              } else {
+                float* pp = a.partial + ((static_cast<int64_t>(it.b) * a.Hq + hq) * a.nsplit + it.split) * (D + 2);
+                pp[r] = oh;
+                if (r == 0) pp[D] = lt > 0.f ? mn : -INFINITY, pp[D + 1] = lt;
+              }
             }
           }
         }
@@ -511,12 +523,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tid == 0 && ctl->abort_flag && a.status) atomicOr(a.status, kStatusWaitExpired);
 }
 
-template <bool BF16>
+template <bool BF16, int D>
 cudaError_t launch_t(int dtype, const DecodeArgs& a, cudaStream_t stream) {
   CUtensorMap tk, tv;
   if (!make_map(&tk, dtype, a.k, D, a.capacity, a.Hkv, a.B, a.ks) || !make_map(&tv, dtype, a.v, D, a.capacity, a.Hkv, a.B, a.vs))
     return cudaErrorInvalidValue;
-  auto kern = decode_tc_kernel<BF16>;
+  auto kern = decode_tc_kernel<BF16, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (e != cudaSuccess) return e;
   int device = 0;
@@ -533,14 +545,15 @@ cudaError_t launch_t(int dtype, const DecodeArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-bool decode_tc_applies(int dtype, int D_, const DecodeArgs& a) {
+bool decode_tc_applies(int dtype, int D, const DecodeArgs& a) {
   const int group = a.Hkv > 0 ? a.Hq / a.Hkv : 0;
-  return dtype != TT_ATTN_F32 && D_ == D && group >= 2 && group <= GP;
+  return dtype != TT_ATTN_F32 && (D == 64 || D == 128) && group >= 2 && group <= GP;
 }
 
 // The scan only; the caller folds the per-split partials (decode.cu's combine kernel).
-cudaError_t launch_decode_tc(int dtype, const DecodeArgs& a, cudaStream_t stream) {
-  return dtype == TT_ATTN_BF16 ? launch_t<true>(dtype, a, stream) : launch_t<false>(dtype, a, stream);
+cudaError_t launch_decode_tc(int dtype, int D, const DecodeArgs& a, cudaStream_t stream) {
+  if (D == 128) return dtype == TT_ATTN_BF16 ? launch_t<true, 128>(dtype, a, stream) : launch_t<false, 128>(dtype, a, stream);
+  return dtype == TT_ATTN_BF16 ? launch_t<true, 64>(dtype, a, stream) : launch_t<false, 64>(dtype, a, stream);
 }
 
 }  // namespace ttattn
