@@ -256,17 +256,11 @@ int tt_attn_decode(const tt_attn_decode_params* p) {
   DeviceGuard guard(p->device);
   if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
   Workspace ws;
-  const size_t base =
-      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   const size_t need =
-      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE_APPEND, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
+      tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);
   if (int rc = ws.acquire(need, p->workspace, p->workspace_bytes, p->alloc, p->device)) return rc;
   a.partial = static_cast<float*>(ws.ptr);
-  a.sched = base >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + base - 256) : nullptr;
-  if (need > base) {
-    a.q_rot = static_cast<char*>(ws.ptr) + base;
-    a.lens_scratch = reinterpret_cast<int32_t*>(static_cast<char*>(ws.ptr) + need - round256(static_cast<size_t>(p->B) * 4));
-  }
+  // the tensor-core path's work counter sits in the last 256 bytes (unused by the scan kernel)
   a.sched = need >= 256 ? reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + need - 256) : nullptr;
   a.status = p->status;
   cudaError_t e = launch_decode(p->dtype, p->D, a, static_cast<cudaStream_t>(p->stream));
