@@ -57,6 +57,8 @@ WORKLOADS = {
     "decode_gqa": dict(kind="decode", dtype="bf16", B=256, Hq=32, Hkv=8, L=1, S=8192, D=128, causal=False, std=1.0),
     "decode_gqa_ncu": dict(kind="decode", dtype="bf16", B=64, Hq=32, Hkv=8, L=1, S=8192, D=128, causal=False, std=1.0),
     "train128_ncu": dict(kind="fwdbwd", dtype="bf16", B=1, Hq=16, Hkv=16, L=4096, S=4096, D=128, causal=True, std=1.0),
+    # a token loop of 32 layers at a small batch, eager and replayed from a CUDA graph (launch-bound)
+    "decode_loop": dict(kind="loop", dtype="bf16", B=8, Hq=32, Hkv=8, S=4096, D=128, layers=32),
     "decode_ncu": dict(kind="decode", dtype="bf16", B=16, Hq=32, Hkv=32, L=1, S=8192, D=128, causal=False, std=1.0),
 }
 ESIZE = {"f32": 4, "f16": 2, "bf16": 2}
@@ -574,6 +576,71 @@ def run_fused_reference_arm(args, w, wname):
     }), flush=True)
 
 
+def run_loop(args, w, wname):
+    """32 layers x (rotary embedding + cache append + grouped-query attention) for one token, per step:
+    eager launches against one CUDA-graph replay.  Value: layer-steps per second through the graph."""
+    import torch
+    from tinytorch_b200 import _capi, op
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, Hq, Hkv, S, D, L = w["B"], w["Hq"], w["Hkv"], w["S"], w["D"], w["layers"]
+    g = torch.Generator(device=dev).manual_seed(99)
+    mk = lambda *s: torch.randn(s, generator=g, device=dev).to(torch.bfloat16)
+    caches = [(mk(B, Hkv, S, D), mk(B, Hkv, S, D)) for _ in range(L)]
+    q, kn, vn = mk(B, Hq, 1, D), mk(B, Hkv, 1, D), mk(B, Hkv, 1, D)
+    lens = torch.full((B,), S // 2, dtype=torch.int32, device=dev)
+    cos, sin = op.ropeTables(S, D, device=dev)
+
+    def step():
+        out = q
+        for kc, vc in caches:
+            out, _, _ = op.sdpAttentionDecodeAppend(out, kn, vn, kc, vc, lens, cos, sin)
+        return out
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3 / n
+
+    t_eager = timed(step, args.steps)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        step()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    t_graph = timed(graph.replay, args.steps)
+    clocks = sampler.stop()
+    nbytes = float(L * B * (S // 2 + 1) * Hkv * D * 2 * 2)
+    print(json.dumps({
+        "metric": "decode layer-steps/s (CUDA graph)", "value": L / t_graph, "unit": "layer-steps/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": 3, "ms_per_step": t_graph * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic (seeded normal)",
+        "config": {"workload": "token loop: %d layers, B=%d Hq=%d Hkv=%d cache %d (half full) D=%d, rotary + append + attention"
+                               % (L, B, Hq, Hkv, S, D)},
+        "eager": {"value": L / t_eager, "unit": "layer-steps/s", "ms_per_step": t_eager * 1e3},
+        "roofline": {"bound": "hbm", "achieved": nbytes / t_graph / 1e9, "peak": measured_peaks()["gbs"], "unit": "GB/s",
+                     "frac": nbytes / t_graph / 1e9 / measured_peaks()["gbs"], "traffic": None,
+                     "peak_source": measured_peaks()["source"], "kernel": "decode_tc_kernel"},
+        "clocks": clocks, "gpu_launches": 4 * L * args.steps,
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -586,7 +653,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if w["kind"] == "fused":
+    if w["kind"] == "loop":
+        run_loop(args, w, args.workload)
+    elif w["kind"] == "fused":
         (run_fused_reference_arm if args.impl == "reference" else run_fused)(args, w, args.workload)
     elif args.impl == "reference":
         run_reference_arm(args, w, args.workload)
