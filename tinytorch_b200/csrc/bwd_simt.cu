@@ -60,7 +60,9 @@ __device__ __forceinline__ void tile_nt(const float* A, const float* B, int ty, 
 }
 
 // delta[b,h,i] = sum_d dO[i,d] * O[i,d].  Each thread reads 16 bytes of a row of
-// O and of dO; the D*sizeof(T)/16 threads of a row reduce with shuffles.
+// O and of dO; the D*sizeof(T)/16 threads of a row reduce with shuffles.  For the
+// tensor-core backward the same pass clears the fp32 dQ accumulator (its TMA
+// reductions need zeros to start from), which saves a separate memset of that size.
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const BwdArgs a) {
   constexpr int N = 16 / sizeof(T);  // elements per thread
@@ -81,6 +83,11 @@ __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const BwdArgs a) {
     const T* gp = reinterpret_cast<const T*>(&gv);
 #pragma unroll
     for (int e = 0; e < N; ++e) s = fmaf(to_f32<T>(op[e]), to_f32<T>(gp[e]), s);
+    if (a.zero_dq_accum) {
+      float4* z = reinterpret_cast<float4*>(a.dq_accum + row * D + part * N);
+#pragma unroll
+      for (int e = 0; e < N / 4; ++e) z[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 #pragma unroll
   for (int of = TPR / 2; of >= 1; of >>= 1) s += __shfl_xor_sync(0xffffffffu, s, of);

@@ -543,9 +543,7 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
       !make_map(&tdo, dtype, a.d_o, D, a.Lq, a.Hq, a.B, a.dos) ||
       !make_map_f32(&tdq, a.dq_accum, D, a.Lq, a.Hq, a.B))
     return cudaErrorInvalidValue;
-  const size_t acc_bytes = static_cast<size_t>(a.B) * a.Hq * a.Lq * D * sizeof(float);
-  cudaError_t e = cudaMemsetAsync(a.dq_accum, 0, acc_bytes, stream);
-  if (e != cudaSuccess) return e;
+  cudaError_t e;  // (dq_accum has been cleared by the delta pre-pass)
   auto kern = bwd_tc_kernel<D, BF16, GEN>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
   if (e != cudaSuccess) return e;
@@ -572,7 +570,9 @@ cudaError_t launch_g(int dtype, int D, const BwdArgs& a, int device, cudaStream_
 }
 
 cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream) {
-  cudaError_t e = launch_bwd_delta(dtype, D, a, stream);
+  BwdArgs pre = a;
+  pre.zero_dq_accum = 1;
+  cudaError_t e = launch_bwd_delta(dtype, D, pre, stream);
   if (e != cudaSuccess) return e;
   const bool general = a.mask.ptr != nullptr || a.causal == TT_ATTN_CAUSAL_BOTTOM_RIGHT;
   return general ? launch_g<true>(dtype, D, a, device, stream) : launch_g<false>(dtype, D, a, device, stream);

@@ -59,7 +59,8 @@ struct BwdArgs {
   const void* d_o;
   const float* lse;
   float* delta;     // workspace [B, Hq, Lq]
-  float* dq_accum;  // workspace [B, Hq, Lq, D] fp32 (tensor-core path), zeroed by the launcher
+  float* dq_accum;  // workspace [B, Hq, Lq, D] fp32 (tensor-core path), zeroed by the delta pre-pass
+  int zero_dq_accum;  // set by the tensor-core launcher: the delta kernel also clears dq_accum
   void* dq;
   void* dk;
   void* dv;
