@@ -80,6 +80,39 @@ def decode_bytes(w, lens):
     return float(int(lens.sum()) * w["Hkv"] * w["D"] * 2 * es + 2 * w["B"] * w["Hq"] * w["D"] * es)
 
 
+def fwd_bytes(w):
+    """Q, K, V read once, O and the fp32 LSE written once."""
+    es = ESIZE[w["dtype"]]
+    q = w["B"] * w["Hq"] * w["L"] * w["D"]
+    kv = w["B"] * w["Hkv"] * w["S"] * w["D"]
+    return float((2 * q + 2 * kv) * es + 4 * w["B"] * w["Hq"] * w["L"])
+
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch over the algorithmic bytes of the same
+# launch, from one ncu capture of a reduced case of each kernel; traffic grows in proportion to the units a launch
+# processes, so the figure reported for a full launch is this ratio times the launch's algorithmic bytes.
+NCU_TRAFFIC_RATIO = {
+    "fwd_tc_kernel": (251.1 / 269.5, "profiles/fwd_tc_kernel_prefill_bf16_S4096_D128.md"),
+    "decode_kernel": (1218.2 / 1213.0, "profiles/decode_kernel_bf16_cap8192_D128.md"),
+    "decode_tc_kernel": (1271.9 / 1248.0, "profiles/decode_tc_kernel_bf16_gqa4_cap8192_D128.md"),
+    "linear_tc_kernel": (88.3 / 100.7, "profiles/linear_tc_kernel_bf16_4096x4096x4096.md"),
+    "add_rms_norm_kernel": (478.5 / 536.9, "profiles/add_rms_norm_kernel_bf16_8192x8192.md"),
+    "silu_mul_kernel": (309.3 / 352.3, "profiles/silu_mul_rows_kernel_bf16_4096x28672.md"),
+}
+
+
+def traffic_of(kernel, algorithmic_bytes):
+    """(bytes per launch, source) scaled from the kernel's ncu capture, or (None, None) without one."""
+    if kernel not in NCU_TRAFFIC_RATIO or algorithmic_bytes is None:
+        return None, None
+    ratio, src = NCU_TRAFFIC_RATIO[kernel]
+    return ratio * algorithmic_bytes, "ncu capture of a reduced case scaled by algorithmic bytes (%s)" % src
+
+
+def nominal_peaks():
+    return dict(tflops=2250.0, gbs=7700.0)
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -335,10 +368,15 @@ def run_ours(args, w, wname):
         res.update(value=per_gpu * world, ms_per_step=sec / steps * 1e3, clocks=clocks, launches=launches * steps,
                    per_gpu=per_gpu, work=work)
         peak = peaks["gbs"] if decode else peaks["tflops"]
+        kern = (("decode_tc_kernel" if wl["Hq"] != wl["Hkv"] else "decode_kernel") if decode
+                else ("fwd_simt_kernel" if wl["dtype"] == "f32" else "fwd_tc_kernel"))
+        alg_bytes = work if decode else (fwd_bytes(wl) if wl["kind"] == "fwd" else None)
+        traffic, traffic_src = traffic_of(kern, alg_bytes)
+        nominal = nominal_peaks()["gbs" if decode else "tflops"]
         res["roofline"] = {"bound": "hbm" if decode else "tensor", "achieved": per_gpu, "peak": peak,
-                           "unit": "GB/s" if decode else "TFLOP/s", "frac": per_gpu / peak, "traffic": None,
-                           "peak_source": peaks["source"],
-                           "kernel": ("decode_tc_kernel" if wl["Hq"] != wl["Hkv"] else "decode_kernel") if decode else ("fwd_simt_kernel" if wl["dtype"] == "f32" else "fwd_tc_kernel")}
+                           "unit": "GB/s" if decode else "TFLOP/s", "frac": per_gpu / peak, "traffic": traffic,
+                           "traffic_source": traffic_src, "algorithmic_bytes": alg_bytes,
+                           "peak_source": peaks["source"], "frac_nominal": per_gpu / nominal, "kernel": kern}
         if with_e2e:
             # public API with HOST buffers: pinned inputs -> device, op, result -> pinned host, every step
             hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
@@ -477,6 +515,9 @@ def run_fused(args, w, wname):
     per_gpu = nbytes * args.steps / sec / div
     peaks = measured_peaks()
     peak = peaks["tflops"] if lin else peaks["gbs"]
+    fused_kernel = "linear_tc_kernel" if lin else ("add_rms_norm_kernel" if rms else "silu_mul_kernel")
+    fused_alg = float((rows * dim + w["n_out"] * dim + rows * w["n_out"]) * ESIZE[w["dtype"]]) if lin else nbytes
+    fused_traffic = traffic_of(fused_kernel, fused_alg)
     line = {
         "metric": "projection TFLOP/s" if lin else w["opname"] + " HBM GB/s", "value": per_gpu * world, "unit": unit,
         "n_gpus": world,
@@ -485,8 +526,9 @@ def run_fused(args, w, wname):
         "config": {"workload": "%s rows=%d dim=%d %s" % (w["opname"], rows, dim, w["dtype"]),
                    "l2": "tensors larger than L2 (no flush)", "sharding": "rows per rank, no collective"},
         "roofline": {"bound": "tensor" if lin else "hbm", "achieved": per_gpu, "peak": peak, "unit": unit,
-                     "frac": per_gpu / peak, "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "linear_tc_kernel" if lin else ("add_rms_norm_kernel" if rms else "silu_mul_kernel")},
+                     "frac": per_gpu / peak, "traffic": fused_traffic[0], "traffic_source": fused_traffic[1],
+                     "peak_source": peaks["source"],
+                     "frac_nominal": per_gpu / nominal_peaks()["tflops" if lin else "gbs"], "kernel": fused_kernel},
         "clocks": clocks, "gpu_launches": args.steps,
     }
     if not args.no_e2e:

@@ -378,7 +378,8 @@ void decode_plan_for(int dtype, int D, int B, int Hq, int Hkv, int capacity, int
     return;
   }
   int ck = 2048;
-  while (ck > 512 && static_cast<long long>(B) * Hkv * ((capacity + ck - 1) / ck) < 296) ck >>= 1;
+  const long long want = D == 64 ? 592 : 296;  // two items per resident CTA (D = 64 runs two CTAs per SM)
+  while (ck > 512 && static_cast<long long>(B) * Hkv * ((capacity + ck - 1) / ck) < want) ck >>= 1;
   if ((capacity + ck - 1) / ck > 64) ck = (((capacity + 63) / 64) + 127) / 128 * 128;
   *chunk = ck;
   *nsplit = capacity <= ck ? 1 : (capacity + ck - 1) / ck;
