@@ -98,6 +98,8 @@ struct DecodeArgs {
   int* sched;                      // tensor-core path: work counter in scratch memory, zeroed by the launcher
   void* q_rot;                     // append on the tensor-core path: scratch [B, Hq, D] for the rotated q
   int32_t* lens_scratch;           // ... and [B] for the lengths after the append
+  int chained;                     // tensor-core path: the kernel before this one in the stream has zeroed the
+                                   // work counter and lets its dependents start early (programmatic launch)
 };
 
 // Each returns a cudaError_t from the launch (no synchronisation).

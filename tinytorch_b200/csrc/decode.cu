@@ -17,6 +17,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace ttattn {
 namespace {
@@ -307,6 +308,7 @@ __global__ void __launch_bounds__(kThreads, G == 1 ? 3 : 1) decode_kernel(const 
 template <typename T, int D>
 __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  ptx::grid_dep_wait();  // (launched early after the tensor-core scan: its partials are complete from here on)
   const float* pp = a.partial + (static_cast<int64_t>(b) * a.Hq + h) * a.nsplit * (D + 2);
   float mn = -INFINITY;
   for (int s = 0; s < a.nsplit; ++s) mn = fmaxf(mn, pp[s * (D + 2) + D]);
@@ -360,10 +362,19 @@ cudaError_t launch_d(int dtype, int D, const DecodeArgs& a, cudaStream_t stream)
   return D == 64 ? launch_t<__nv_bfloat16, 64, APPEND>(a, stream) : launch_t<__nv_bfloat16, 128, APPEND>(a, stream);
 }
 
+// `early`: the scan kernel before it lets its dependents start (tensor-core path); the combine kernel's CTAs
+// then come up while the scan still runs and wait in grid_dep_wait() for its partials.
 template <typename T, int D>
-cudaError_t combine_t(const DecodeArgs& a, cudaStream_t stream) {
-  decode_combine_kernel<T, D><<<dim3(a.Hq, a.B), D, 0, stream>>>(a);
-  return cudaGetLastError();
+cudaError_t combine_t(const DecodeArgs& a, cudaStream_t stream, bool early = false) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.Hq, a.B);
+  cfg.blockDim = dim3(D);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (early) cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_combine_kernel<T, D>, a);
 }
 
 // The plan a call with these sizes uses (the launcher, the workspace query and the entry points agree
@@ -390,8 +401,8 @@ cudaError_t launch_decode(int dtype, int D, const DecodeArgs& a, cudaStream_t st
     // several query heads per kv head: the tensor-core scan, then the same combine kernel
     cudaError_t e = launch_decode_tc(dtype, D, a, stream);
     if (e != cudaSuccess || a.nsplit == 1) return e;
-    if (D == 128) return dtype == TT_ATTN_F16 ? combine_t<__half, 128>(a, stream) : combine_t<__nv_bfloat16, 128>(a, stream);
-    return dtype == TT_ATTN_F16 ? combine_t<__half, 64>(a, stream) : combine_t<__nv_bfloat16, 64>(a, stream);
+    if (D == 128) return dtype == TT_ATTN_F16 ? combine_t<__half, 128>(a, stream, true) : combine_t<__nv_bfloat16, 128>(a, stream, true);
+    return dtype == TT_ATTN_F16 ? combine_t<__half, 64>(a, stream, true) : combine_t<__nv_bfloat16, 64>(a, stream, true);
   }
   return launch_d<false>(dtype, D, a, stream);
 }
@@ -405,6 +416,8 @@ namespace {
 template <typename T, int D>
 __global__ void __launch_bounds__(D / 2) rope_append_kernel(const DecodeArgs a, int32_t* lens_out) {
   const int hh = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+  ptx::grid_dep_launch();  // the decode kernel may set itself up; it waits for this grid before it reads anything
+  if (hh == 0 && b == 0 && t == 0 && a.sched) *a.sched = 0;  // its work counter
   int pos = a.kv_lens[b];
   pos = pos < 0 ? 0 : pos;
   const bool room = pos < a.capacity;
@@ -449,6 +462,7 @@ cudaError_t append_tc_t(int dtype, const DecodeArgs& a, cudaStream_t stream) {
   d.q = a.q_rot;
   d.qs = Str3{static_cast<int64_t>(a.Hq) * D, D, D};
   d.kv_lens = a.lens_scratch;
+  d.chained = 1;
   return launch_decode(dtype, D, d, stream);
 }
 

@@ -172,6 +172,10 @@ __global__ void __launch_bounds__(kThreads, OCC)
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t tS = tmem, tO = tmem + 2 * GP;  // buffer i of each at + 16 i
+  // Everything above touched no global memory.  In a chained launch the kernel before this one (rotation and
+  // append) may still be running: wait for its results, then let the combine kernel's CTAs come up.
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
 
   if (warp == kProducerWarp) {
     // -------------------------------------------------------------- producer --
@@ -548,11 +552,22 @@ cudaError_t launch_g(int dtype, const DecodeArgs& a, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   const long long n_items = static_cast<long long>(a.B) * a.Hkv * a.nsplit;
   if (n_items > 0x7fffffffll || !a.sched) return cudaErrorInvalidValue;
-  e = cudaMemsetAsync(a.sched, 0, sizeof(int), stream);  // the work counter starts at zero for every launch
-  if (e != cudaSuccess) return e;
   const int ctas = OCC * sm_count(device);
-  kern<<<static_cast<unsigned>(n_items < ctas ? n_items : ctas), kThreads, kSmem, stream>>>(tk, tv, a, static_cast<int>(n_items));
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(n_items < ctas ? n_items : ctas));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (a.chained) {
+    cfg.attrs = attr, cfg.numAttrs = 1;
+  } else {
+    e = cudaMemsetAsync(a.sched, 0, sizeof(int), stream);  // the work counter starts at zero for every launch
+    if (e != cudaSuccess) return e;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, tk, tv, a, static_cast<int>(n_items));
 }
 
 template <bool BF16, int D, int OCC>

@@ -358,6 +358,13 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may start
+// while the kernel before it in the stream still runs; it must not touch that kernel's results before
+// grid_dep_wait(), which returns once the earlier grid has completed and its writes are visible (and at once
+// in a kernel launched the ordinary way).  grid_dep_launch() in the earlier kernel lets the later one start.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
