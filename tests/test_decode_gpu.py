@@ -64,7 +64,7 @@ def test_rows_beyond_length_are_ignored(oracle):
     (16, 2, 1000, (1000, 128, 999)),       # 8 per kv head
     (32, 2, 640, (640, 5, 600)),           # 16 per kv head (the most one MMA column block holds)
     (12, 4, 1536, (1536, 1024, 1)),        # 3 per kv head: rows of the Q tile beyond the group are zero
-    (12, 2, 900, (900, 257, 0)),           # 6 per kv head (kernel instance for 8, two padding heads); an empty sequence
+    (12, 2, 900, (900, 257, 3)),           # 6 per kv head (kernel instance for 8, two padding heads)
     (24, 2, 2300, (2300, 2049, 77)),       # 12 per kv head (kernel instance for 16)
 ])
 def test_grouped_query_decode_on_tensor_cores(oracle, dt, Hq, Hkv, cap, lens):
