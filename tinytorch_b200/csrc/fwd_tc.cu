@@ -296,7 +296,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       // thread execute in issue order, so QK(t,j+1) overwriting S_t / P_t cannot
       // pass PV(t,j) that still reads P_t, and the first QK of the next item
       // cannot pass the last PV of this one.
-      if (lane == 0) {
+      // The whole warp runs the loop (waits included, made uniform by a vote); one elected lane issues.
+      {
+        const bool leader = ptx::elect_one();
+        auto uwait = [&](uint64_t* bar, uint32_t parity) {
+          return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
+        };
         // A negative scale is folded into the sign of Q so that the softmax
         // always works with a non-negative multiplier.
         const uint32_t neg = a.scale < 0.f ? (1u << 13) : 0u;
@@ -315,18 +320,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t qc = 0;        // items with work seen so far (q_full phase)
         bool ok = true;
 
-        auto wait_k = [&](uint32_t g) {
-          return ptx::mbar_wait(&ctl->k_full[g % NSTAGE], (g / NSTAGE) & 1, abort_flag);
-        };
+        auto wait_k = [&](uint32_t g) { return uwait(&ctl->k_full[g % NSTAGE], (g / NSTAGE) & 1); };
         auto issue_qk = [&](int t, uint32_t g) {
           const uint32_t a0 = qlo + t * (TB >> 4), b0 = klo + (g % NSTAGE) * (TB >> 4), d = tmem + t * 128;
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             // K-major operands: 64-element halves HALF_BYTES apart, 32 bytes per k-step
             const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
-            ptx::mma_ss2(d, a0 + off, kHi, b0 + off, kHi, idesc_qk, ks > 0 ? 1u : 0u);
+            if (leader) ptx::mma_ss2(d, a0 + off, kHi, b0 + off, kHi, idesc_qk, ks > 0 ? 1u : 0u);
           }
-          ptx::mma_commit(&ctl->s_full[t]);
+          if (leader) ptx::mma_commit(&ctl->s_full[t]);
         };
         auto issue_pv = [&](int t, uint32_t g, bool first) {
           const uint32_t b0 = vlo + (g % NSTAGE) * (TB >> 4), d = tmem + 256 + t * D, a0 = tmem + t * 128;
@@ -334,30 +337,31 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int ks = 0; ks < BN / 16; ++ks) {
             // V is N(=D)-contiguous: 16 keys per k-step = 2048 bytes; the two
             // 64-wide column blocks of D=128 are HALF_BYTES apart (LBO).
-            ptx::mma_ts2(d, a0 + ks * 8, b0 + ks * (2048 >> 4), kHi, idesc_pv, (!first || ks > 0) ? 1u : 0u);
+            if (leader) ptx::mma_ts2(d, a0 + ks * 8, b0 + ks * (2048 >> 4), kHi, idesc_pv, (!first || ks > 0) ? 1u : 0u);
           }
         };
 
         for (uint32_t i = 0; ok; ++i) {
           const int slot = i & 1;
-          if (!ptx::mbar_wait(&ctl->item_full[slot], (i >> 1) & 1, abort_flag)) break;
+          if (!uwait(&ctl->item_full[slot], (i >> 1) & 1)) break;
           const int w = ctl->item[slot];
-          ptx::mbar_arrive(&ctl->item_empty[slot]);
+          __syncwarp();  // every lane has read the slot before it is handed back
+          if (leader) ptx::mbar_arrive(&ctl->item_empty[slot]);
           if (w < 0) break;
           const Item it = decode_item<GEN>(a, w, n_pairs);
           if (it.n_max == 0) continue;
           const int nt0 = it.nt0, nt1 = it.nt1, n_max = it.n_max;
           auto nt = [&](int t) { return t == 0 ? nt0 : nt1; };
 
-          if (!(ok = ptx::mbar_wait(&ctl->q_full, qc & 1, abort_flag))) break;
+          if (!(ok = uwait(&ctl->q_full, qc & 1))) break;
           ++qc;
           if (!(ok = wait_k(g0))) break;
           ptx::tc_fence_after();
 #pragma unroll
           for (int t = 0; t < QT; ++t)
             if (nt(t) > 0) issue_qk(t, g0);
-          ptx::mma_commit(&ctl->k_empty[g0 % NSTAGE]);
-          if (n_max == 1) ptx::mma_commit(&ctl->q_empty);
+          if (leader) ptx::mma_commit(&ctl->k_empty[g0 % NSTAGE]);
+          if (leader && n_max == 1) ptx::mma_commit(&ctl->q_empty);
 
           for (int j = 0; j < n_max && ok; ++j) {
             const uint32_t g = g0 + j;
@@ -368,19 +372,19 @@ __global__ void __launch_bounds__(kThreads, 1)
               const bool do_pv = j < nt(t), do_qk = j + 1 < nt(t);
               // all waits first, then the MMAs of this tile back to back
               if (do_pv) {
-                if (!(ok = ptx::mbar_wait(&ctl->v_full[g % NSTAGE], (g / NSTAGE) & 1, abort_flag))) break;
-                if (!(ok = ptx::mbar_wait(&ctl->p_full[t], ((t == 0 ? c0 : c1) + j) & 1, abort_flag))) break;
+                if (!(ok = uwait(&ctl->v_full[g % NSTAGE], (g / NSTAGE) & 1))) break;
+                if (!(ok = uwait(&ctl->p_full[t], ((t == 0 ? c0 : c1) + j) & 1))) break;
               }
               if (do_qk && !(ok = wait_k(g + 1))) break;
               ptx::tc_fence_after();
               if (do_pv) {
                 issue_pv(t, g, j == 0);
-                if (j == nt(t) - 1) ptx::mma_commit(&ctl->o_full[t]);
-                if (t == last_pv) ptx::mma_commit(&ctl->v_empty[g % NSTAGE]);
+                if (leader && j == nt(t) - 1) ptx::mma_commit(&ctl->o_full[t]);
+                if (leader && t == last_pv) ptx::mma_commit(&ctl->v_empty[g % NSTAGE]);
               }
               if (do_qk) {
                 issue_qk(t, g + 1);
-                if (t == last_qk) {
+                if (leader && t == last_qk) {
                   ptx::mma_commit(&ctl->k_empty[(g + 1) % NSTAGE]);
                   if (j + 2 == n_max) ptx::mma_commit(&ctl->q_empty);  // last QK of the item
                 }
