@@ -370,12 +370,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int t = 0; t < QT; ++t) {
               const bool do_pv = j < nt(t), do_qk = j + 1 < nt(t);
-              // all waits first, then the MMAs of this tile back to back
-              if (do_pv) {
-                if (!(ok = uwait(&ctl->v_full[g % NSTAGE], (g / NSTAGE) & 1))) break;
-                if (!(ok = uwait(&ctl->p_full[t], ((t == 0 ? c0 : c1) + j) & 1))) break;
-              }
-              if (do_qk && !(ok = wait_k(g + 1))) break;
+              // all waits first, then the MMAs of this tile back to back; the wait for P comes last: it is
+              // the one on the critical path (softmax -> PV -> next QK -> softmax), the tiles are long there
+              // (one vote for the three: between them the lanes only poll)
+              bool okb = true;
+              if (do_pv) okb = ptx::mbar_wait(&ctl->v_full[g % NSTAGE], (g / NSTAGE) & 1, abort_flag);
+              if (do_qk && okb) okb = ptx::mbar_wait(&ctl->k_full[(g + 1) % NSTAGE], ((g + 1) / NSTAGE) & 1, abort_flag);
+              if (do_pv && okb) okb = ptx::mbar_wait(&ctl->p_full[t], ((t == 0 ? c0 : c1) + j) & 1, abort_flag);
+              if (!(ok = __all_sync(0xffffffffu, okb) != 0)) break;
               ptx::tc_fence_after();
               if (do_pv) {
                 issue_pv(t, g, j == 0);
