@@ -213,7 +213,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 17) {
     // ---------------------------------------------------------------- issuer --
-    if (lane == 0 && n_steps > 0) {
+    // The whole warp runs the loop (waits made uniform by a vote); one elected lane issues, so that addresses
+    // and descriptors stay warp-uniform.
+    if (n_steps > 0) {
+      const bool leader = ptx::elect_one();
+      auto uwait = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
+      };
       constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
       const uint32_t fmt = BF16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ, fmt, 0, 0);   // S^T, dP^T: N = queries
@@ -222,26 +228,26 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
       const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
       const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK), kHalfBytes);
-      bool ok = ptx::mbar_wait(&ctl->kv_full, 0, abort_flag);
+      bool ok = uwait(&ctl->kv_full, 0);
       auto stage_lo = [&](const uint8_t* base, int n, uint32_t lbo) {
         return ptx::smem_desc_lo(ptx::smem_u32(base + (n % NQ) * TB), lbo);
       };
       // S^T = K Q^T and dP^T = V dO^T of step n
       auto issue_s_dp = [&](int n) {
-        if (!ptx::mbar_wait(&ctl->q_full[n % NQ], (n / NQ) & 1, abort_flag)) return false;
+        if (!uwait(&ctl->q_full[n % NQ], (n / NQ) & 1)) return false;
         ptx::tc_fence_after();
         const uint32_t qlo = stage_lo(sQ, n, 16), dolo = stage_lo(sdO, n, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
         }
-        ptx::mma_commit(&ctl->sp_full);
+        if (leader) ptx::mma_commit(&ctl->sp_full);
         return true;
       };
       if (ok) ok = issue_s_dp(0);
@@ -254,56 +260,56 @@ __global__ void __launch_bounds__(kThreads, 1)
         // odd ones are still being computed.
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          if (!(ok = ptx::mbar_wait(half == 0 ? &ctl->pds_half : &ctl->pds_full, n & 1, abort_flag))) break;
+          if (!(ok = uwait(half == 0 ? &ctl->pds_half : &ctl->pds_full, n & 1))) break;
           ptx::tc_fence_after();
 #pragma unroll
           for (int ks = half; ks < BQ / 16; ks += 2)
-            ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+            if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
                          (n > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
           for (int ks = half; ks < BQ / 16; ks += 2)
-            ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+            if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
                          (n > 0 || ks > 0) ? 1u : 0u);
         }
         if (!ok) break;
-        if (!kPipe) ptx::mma_commit(&ctl->q_empty[st]);  // Q and dO of this step have been read (dV, dK above)
+        if (!kPipe) if (leader) ptx::mma_commit(&ctl->q_empty[st]);  // Q and dO of this step have been read (dV, dK above)
         if (kPipe) {
           // P^T / dS^T of this step have been consumed from TMEM (in issue order):
           // the next step's S^T / dP^T go first, then this step's dQ, which reads
           // dS^T from shared memory
           if (n + 1 < n_steps && !(ok = issue_s_dp(n + 1))) break;
-          if (n >= 2 && !(ok = ptx::mbar_wait(&ctl->dq_free[n & 1], ((n >> 1) - 1) & 1, abort_flag))) break;
+          if (n >= 2 && !(ok = uwait(&ctl->dq_free[n & 1], ((n >> 1) - 1) & 1))) break;
         }
 #pragma unroll
         for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
-          ptx::mma_ss2(tdQ(n), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_ss2(tdQ(n), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
         }
-        ptx::mma_commit(&ctl->dq_full[kPipe ? (n & 1) : 0]);
-        if (kPipe) ptx::mma_commit(&ctl->q_empty[st]);
+        if (leader) ptx::mma_commit(&ctl->dq_full[kPipe ? (n & 1) : 0]);
+        if (kPipe) if (leader) ptx::mma_commit(&ctl->q_empty[st]);
         if (!kPipe && n + 1 < n_steps) {
           // (the single Q / dO stage was handed back after dK above, so its reload runs under
           // the dQ MMAs and the read-out.)  dP^T of the next step can go into region B at once:
           // dS^T there has been consumed in issue order.  Region A holds this step's dQ until the
           // compute threads have read it: S^T of the next step waits for that.
-          if (!(ok = ptx::mbar_wait(&ctl->q_full[(n + 1) % NQ], ((n + 1) / NQ) & 1, abort_flag))) break;
+          if (!(ok = uwait(&ctl->q_full[(n + 1) % NQ], ((n + 1) / NQ) & 1))) break;
           ptx::tc_fence_after();
           const uint32_t qlo = stage_lo(sQ, n + 1, 16), dolo = stage_lo(sdO, n + 1, 16);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-            ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+            if (leader) ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
           }
-          if (!(ok = ptx::mbar_wait(&ctl->dq_free[0], n & 1, abort_flag))) break;
+          if (!(ok = uwait(&ctl->dq_free[0], n & 1))) break;
           ptx::tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-            ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+            if (leader) ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
           }
-          ptx::mma_commit(&ctl->sp_full);
+          if (leader) ptx::mma_commit(&ctl->sp_full);
         }
       }
-      if (ok) ptx::mma_commit(&ctl->acc_full);
+      if (ok) if (leader) ptx::mma_commit(&ctl->acc_full);
     }
   } else {
     // --------------------------------------------------------------- compute --
