@@ -134,7 +134,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- issuer --
-    if (lane == 0) {
+    // the whole warp runs the loop (waits made uniform by a vote), one elected lane issues: addresses and
+    // descriptors stay warp-uniform
+    {
+      const bool leader = ptx::elect_one();
       constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
       const uint32_t idesc = ptx::make_idesc_f16(BM, BN, BF16 ? 1 : 0, 0, 0);
       const uint32_t alo = ptx::smem_desc_lo(ptx::smem_u32(smem), 16);
@@ -145,20 +148,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++i) {
         const int buf = i & 1;
         // the epilogue has read this accumulator's previous tile
-        if (!(ok = ptx::mbar_wait(&ctl->acc_empty[buf], ((i >> 1) & 1) ^ 1, abort_flag))) break;
+        if (!(ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->acc_empty[buf], ((i >> 1) & 1) ^ 1, abort_flag)) != 0)) break;
         ptx::tc_fence_after();
         const uint32_t d = tmem + buf * BN;
         for (int kb = 0; kb < n_kb; ++kb, ++g) {
           const int s = g % NSTAGE;
-          if (!(ok = ptx::mbar_wait(&ctl->full[s], (g / NSTAGE) & 1, abort_flag))) break;
+          if (!(ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->full[s], (g / NSTAGE) & 1, abort_flag)) != 0)) break;
           ptx::tc_fence_after();
           const uint32_t so = s * (kStageBytes >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)  // 32 bytes per k-step inside the 128-byte swizzled row
-            ptx::mma_ss2(d, alo + so + k * 2, kHi, blo + so + k * 2, kHi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          ptx::mma_commit(&ctl->empty[s]);
+            if (leader) ptx::mma_ss2(d, alo + so + k * 2, kHi, blo + so + k * 2, kHi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          if (leader) ptx::mma_commit(&ctl->empty[s]);
         }
-        if (ok) ptx::mma_commit(&ctl->acc_full[buf]);
+        if (ok && leader) ptx::mma_commit(&ctl->acc_full[buf]);
       }
     }
   } else if (warp >= 4) {
