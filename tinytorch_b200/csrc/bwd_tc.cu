@@ -50,6 +50,7 @@ struct __align__(8) SmemCtl {
   uint64_t q_full[2], q_empty[2];
   uint64_t sp_full, pds_half, pds_full, acc_full;  // pds_half: the first 16 queries of every warpgroup are done
   uint64_t dq_full[2], dq_free[2];  // per dQ buffer
+  uint64_t vec_full[2];             // per-query vectors of a step are in shared memory (written by warpgroup 0)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -153,6 +154,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::mbar_init(&ctl->pds_full, kCompute);
     ptx::mbar_init(&ctl->pds_half, kCompute);
     ptx::mbar_init(&ctl->acc_full, 1);
+    ptx::mbar_init(&ctl->vec_full[0], BM);
+    ptx::mbar_init(&ctl->vec_full[1], BM);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&ctl->dq_full[i], 1);
@@ -346,6 +349,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       float l0, d0;
       load_vec(0, l0, d0);
       store_vec(0, l0, d0);
+      ptx::mbar_arrive(&ctl->vec_full[0]);
     }
     // dQ of step n -> global; thread r owns query row q0 + r, warpgroup w the columns
     // [32w, 32w+32) (D = 64: warpgroups 0 and 1; D = 128: all four): through a swizzled
@@ -385,7 +389,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (wg == 0 && n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
       // all threads reach this point every step, expired waits included
       TT_BSTAMP(wg, 0);
-      ptx::named_barrier(1, kCompute);  // this step's vectors are in shared memory
+      // This step's vectors are in shared memory.  (An mbarrier, not a barrier over the four warpgroups: the two
+      // that drain dQ take longer per step, and the others may go on into the next step's exponentials meanwhile.
+      // Warpgroup 0 cannot overwrite a buffer that is still read: it writes buffer n & 1 again after the first
+      // MMAs of step n + 1 have completed, which every warpgroup's results of step n precede.)
+      if (ok) ok = ptx::mbar_wait(&ctl->vec_full[n & 1], (n >> 1) & 1, abort_flag);
       if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
       TT_BSTAMP(wg, 2);
       ptx::tc_fence_after();
@@ -463,7 +471,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::tc_fence_before();
       ptx::mbar_arrive(&ctl->pds_full);
       TT_BSTAMP(wg, 4);
-      if (wg == 0 && n + 1 < n_steps) store_vec(n + 1, ln, dn);
+      if (wg == 0 && n + 1 < n_steps) {
+        store_vec(n + 1, ln, dn);
+        ptx::mbar_arrive(&ctl->vec_full[(n + 1) & 1]);
+      }
       // dQ: of the previous step while this step's MMAs run (kPipe), else of this step
       if (kPipe) {
         if (wg < 2 && n >= 1) read_out_dq(n - 1);
