@@ -387,5 +387,19 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 2^x on the FMA and integer pipes (no MUFU): x = n + f with n = round(x), f in [-0.5, 0.5]; a cubic for 2^f
+// (maximum relative error 7.5e-5, below half a unit in the last place of fp16 and bf16) and n added to the exponent
+// field.  Arguments below -126 (-inf included) give a value below 2^-125; NaN gives that too.  For kernels whose
+// exponentials are bound by the four MUFU units of an SM sub-partition: a share of them goes here.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -126.f);
+  const float magic = 12582912.f;  // 1.5 * 2^23: the sum holds round(x) in its low mantissa bits
+  const float xr = x + magic;
+  const float f = x - (xr - magic);
+  const float p = fmaf(fmaf(fmaf(0.055171750485897064f, f, 0.24261131882667542f), f, 0.6932609677314758f), f,
+                       0.9999280571937561f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
 }  // namespace ptx
 }  // namespace ttattn
