@@ -362,6 +362,17 @@ def run_ours(args, w, wname):
             sampler.start()
         sec = timed(fn, steps, warmup)
         clocks = sampler.stop() if rank == 0 else {}
+        if rank == 0 and world == 1:
+            # The timed region is a few milliseconds, shorter than the sampler's period.  One untimed second of
+            # the same launches afterwards shows the clocks and throttle reasons this kernel settles at.
+            probe = ClockSampler(local)
+            probe.start()
+            t_end = time.time() + 1.0
+            while time.time() < t_end:
+                for _ in range(20):
+                    fn()
+                torch.cuda.synchronize()
+            clocks["sustained_probe"] = probe.stop()
         decode = wl["kind"] == "decode"
         div = 1e9 if decode else 1e12
         per_gpu = work * steps / sec / div
