@@ -26,7 +26,7 @@
 // (key tile, query tile) pair is added to an fp32 buffer through swizzled staging
 // tiles and TMA reductions (cp.reduce.async.bulk.tensor ... add) and converted to
 // the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
-// with TMA (128-byte swizzle, one copy per CTA), one thread of warp 17 issues the MMAs;
+// with TMA (128-byte swizzle, one copy per CTA), warp 17 runs the issuing loop with one elected lane issuing the MMAs;
 // every wait is bounded.
 #include <type_traits>
 

@@ -16,7 +16,8 @@
 //               item ahead of its loads), writes the empty result of items without keys
 //               itself, and streams K / V tiles of 128 keys through a 3-stage TMA ring
 //               that runs on across items, so HBM never waits for a prologue or epilogue
-//   warp 9      issuer: one thread issues the MMAs, one first-MMA ahead of the softmax
+//   warp 9      issuer: one thread issues the MMAs, one first-MMA ahead of the softmax (with 16 small
+//               MMAs behind three waits per tile a warp-wide loop with an elected lane was slower here)
 //   warps 0-3,  two softmax warpgroups that take the tiles alternately (tile t belongs to
 //   warps 4-7   warpgroup t & 1), each with its own S^T / P buffers, its own O^T
 //               accumulator and its own running maximum and sum per head: two independent

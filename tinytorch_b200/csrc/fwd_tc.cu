@@ -14,7 +14,8 @@
 //                       two Q tiles and of each K and V tile into a 2-stage ring.
 //                       It runs ahead: the next item's Q and first K/V tiles are
 //                       requested while the current item is still being computed.
-//   warp 9   issuer   : one thread issues tcgen05.mma; S_t = Q_t.K^T accumulates in
+//   warp 9   issuer   : the warp runs the issuing loop, one elected lane issues tcgen05.mma
+//                       (warp-uniform descriptors); S_t = Q_t.K^T accumulates in
 //                       TMEM columns [t*128, t*128+128), O_t += P_t.V in columns
 //                       [256 + t*D, 256 + (t+1)*D).  The two tiles are interleaved
 //                       (PV_0 QK_0' PV_1 QK_1') so that the tensor pipe computes for

@@ -6,7 +6,7 @@
 // Persistent kernel, one CTA per SM, 128 x 256 output tiles:
 //   warp 0     producer: cp.async.bulk.tensor loads (128-byte swizzle) of the 128 x 64
 //              slice of x and the 256 x 64 slice of w into a 4-stage ring
-//   warp 1     issuer: one thread issues tcgen05.mma (kind::f16, M = 128, N = 256, both
+//   warp 1     issuer: the warp runs the loop, one elected lane issues tcgen05.mma (kind::f16, M = 128, N = 256, both
 //              operands K-major) into one of TWO 256-column TMEM accumulators, so that
 //              the epilogue of a tile runs under the main loop of the next
 //   warps 4-7  epilogue: thread r owns output row r (TMEM lane r); 64 columns at a time
