@@ -115,6 +115,7 @@ __device__ __forceinline__ void rope_slice(float (&x)[N], const float* cos, cons
 // attended to like any other row; q is rotated to the same position.
 template <typename T, int D, int G, bool APPEND>
 __global__ void __launch_bounds__(kThreads, G == 1 ? 3 : 1) decode_kernel(const DecodeArgs a) {
+  ptx::grid_dep_launch();  // the combine kernel's CTAs may come up under the last wave of this grid
   constexpr int N = Vec16<T>::N;  // elements per 16-byte slice
   constexpr int LPK = D / N;      // lanes per cache row
   constexpr int KPW = 32 / LPK;   // rows per warp-wide load
@@ -324,6 +325,21 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeArgs a) {
   if (a.lse && d == 0) a.lse[static_cast<int64_t>(b) * a.Hq + h] = lt > 0.f ? (mn + log2f(lt)) * kLn2 : -INFINITY;
 }
 
+// `early`: the scan kernel before it lets its dependents start; the combine kernel's CTAs
+// then come up while the scan still runs and wait in grid_dep_wait() for its partials.
+template <typename T, int D>
+cudaError_t combine_t(const DecodeArgs& a, cudaStream_t stream, bool early = false) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.Hq, a.B);
+  cfg.blockDim = dim3(D);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (early) cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_combine_kernel<T, D>, a);
+}
+
 template <typename T, int D, bool APPEND>
 cudaError_t launch_t(const DecodeArgs& a, cudaStream_t stream) {
   const int group = a.Hq / a.Hkv;
@@ -338,8 +354,7 @@ cudaError_t launch_t(const DecodeArgs& a, cudaStream_t stream) {
     decode_kernel<T, D, 1, APPEND><<<grid, kThreads, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || a.nsplit == 1) return e;
-  decode_combine_kernel<T, D><<<dim3(a.Hq, a.B), D, 0, stream>>>(a);
-  return cudaGetLastError();
+  return combine_t<T, D>(a, stream, true);
 }
 
 }  // namespace
@@ -360,21 +375,6 @@ cudaError_t launch_d(int dtype, int D, const DecodeArgs& a, cudaStream_t stream)
   if (dtype == TT_ATTN_F16)
     return D == 64 ? launch_t<__half, 64, APPEND>(a, stream) : launch_t<__half, 128, APPEND>(a, stream);
   return D == 64 ? launch_t<__nv_bfloat16, 64, APPEND>(a, stream) : launch_t<__nv_bfloat16, 128, APPEND>(a, stream);
-}
-
-// `early`: the scan kernel before it lets its dependents start (tensor-core path); the combine kernel's CTAs
-// then come up while the scan still runs and wait in grid_dep_wait() for its partials.
-template <typename T, int D>
-cudaError_t combine_t(const DecodeArgs& a, cudaStream_t stream, bool early = false) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(a.Hq, a.B);
-  cfg.blockDim = dim3(D);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  if (early) cfg.attrs = attr, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, decode_combine_kernel<T, D>, a);
 }
 
 // The plan a call with these sizes uses (the launcher, the workspace query and the entry points agree
