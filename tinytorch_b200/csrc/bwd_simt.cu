@@ -15,6 +15,7 @@
 //                      registers -> deterministic, no atomics
 //   bwd_dq_kernel      one CTA per 64-query tile: loops over key tiles, accumulates dQ
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace ttattn {
 namespace {
@@ -65,6 +66,7 @@ __device__ __forceinline__ void tile_nt(const float* A, const float* B, int ty, 
 // reductions need zeros to start from), which saves a separate memset of that size.
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const BwdArgs a) {
+  ptx::grid_dep_launch();  // the tensor-core backward kernel may set itself up and start on Q, K, V, dO meanwhile
   constexpr int N = 16 / sizeof(T);  // elements per thread
   constexpr int TPR = D / N;         // threads per row (8, 16 or 32)
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) / TPR;

@@ -324,6 +324,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float c = a.scale * kLog2e;
     const float2 c2v = make_float2(c, c), sc2 = make_float2(a.scale, a.scale);
     bool ok = true;
+    // This kernel is launched early behind the delta pre-pass: loads, barriers, TMEM and the first S^T / dP^T
+    // MMAs need only the inputs; delta and the cleared dQ accumulator are first touched by these threads.
+    ptx::grid_dep_wait();
+    ptx::grid_dep_launch();  // (the conversion kernel may come up; it waits for this grid)
 
     // per-query vectors of step n live in svec[(n & 1)]: [0,128) -lse * log2(e), [128,256) -delta * scale;
     // warpgroup 0 fetches them one step ahead.  load_vec only issues the two loads (raw values: nothing
@@ -536,6 +540,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // dq_accum (fp32, dense [B,Hq,Lq,D]) -> dq (tensor dtype, strided)
 template <typename T, int D>
 __global__ void __launch_bounds__(256) dq_convert_kernel(const BwdArgs a) {
+  ptx::grid_dep_wait();  // launched early: the accumulator is complete from here on
   const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -567,13 +572,25 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
   if (e != cudaSuccess) return e;
   dim3 grid((a.Skv + BM - 1) / BM, a.Hkv, a.B);
-  kern<<<grid, kThreads, Cfg<D>::kSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
-  e = cudaGetLastError();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Cfg<D>::kSmem;
+  cfg.stream = stream;
+  cfg.attrs = attr, cfg.numAttrs = 1;  // early launch behind the delta pre-pass
+  e = cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tdo, tdq, a);
   if (e != cudaSuccess || !a.dq) return e;
   const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
   const int blocks = static_cast<int>((total + 255) / 256 < 8 * sm_count(device) ? (total + 255) / 256 : 8 * sm_count(device));
-  dq_convert_kernel<T, D><<<blocks, 256, 0, stream>>>(a);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cv = {};
+  cv.gridDim = dim3(blocks);
+  cv.blockDim = dim3(256);
+  cv.stream = stream;
+  cv.attrs = attr, cv.numAttrs = 1;
+  return cudaLaunchKernelEx(&cv, dq_convert_kernel<T, D>, a);
 }
 
 }  // namespace
