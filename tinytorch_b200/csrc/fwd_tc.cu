@@ -14,8 +14,7 @@
 //                       two Q tiles and of each K and V tile into a 2-stage ring.
 //                       It runs ahead: the next item's Q and first K/V tiles are
 //                       requested while the current item is still being computed.
-//   warp 9   issuer   : the warp runs the issuing loop, one elected lane issues tcgen05.mma
-//                       (warp-uniform descriptors); S_t = Q_t.K^T accumulates in
+//   warp 9   issuer   : one thread issues tcgen05.mma; S_t = Q_t.K^T accumulates in
 //                       TMEM columns [t*128, t*128+128), O_t += P_t.V in columns
 //                       [256 + t*D, 256 + (t+1)*D).  The two tiles are interleaved
 //                       (PV_0 QK_0' PV_1 QK_1') so that the tensor pipe computes for
@@ -73,11 +72,12 @@ constexpr int kItemConsumers = 1 + QT * BM;  // issuer thread + every softmax th
 #endif
 
 struct __align__(8) SmemCtl {
-  uint64_t q_full, q_empty;
+  uint64_t q_full[QT], q_empty[QT];  // per query tile: tile 0 of the next item is loaded while tile 1 still works
   uint64_t k_full[NSTAGE], k_empty[NSTAGE], v_full[NSTAGE], v_empty[NSTAGE];
   uint64_t s_full[QT], p_full[QT], o_full[QT];
   uint64_t item_full[2], item_empty[2];
   int item[2];
+  int item_nt0[2];  // key tiles of query tile 0 of the published item (the issuer's look-ahead needs only this)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -209,8 +209,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr int HALF_BYTES = BM * 128;
 
   if (warp == 8 && lane == 0) {
-    ptx::mbar_init(&ctl->q_full, 1);
-    ptx::mbar_init(&ctl->q_empty, 1);
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+      ptx::mbar_init(&ctl->q_full[t], 1);
+      ptx::mbar_init(&ctl->q_empty[t], 1);
+    }
 #pragma unroll
     for (int i = 0; i < NSTAGE; ++i) {
       ptx::mbar_init(&ctl->k_full[i], 1);
@@ -252,28 +255,34 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 8) {
       // ---------------------------------------------------------- producer --
       if (lane == 0) {
-        uint32_t g = 0;   // K/V tiles requested so far (ring position)
-        uint32_t qc = 0;  // items whose Q was requested so far
+        uint32_t g = 0;             // K/V tiles requested so far (ring position)
+        uint32_t qc0 = 0, qc1 = 0;  // items whose Q tile 0 / 1 was requested so far
         for (uint32_t i = 0;; ++i) {
           int w = atomicAdd(a.sched, 1);
           if (w >= n_items) w = -1;
           const int slot = i & 1;
+          Item it{};
+          if (w >= 0) it = decode_item<GEN>(a, w, n_pairs);
           if (!ptx::mbar_wait(&ctl->item_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag)) break;
           ctl->item[slot] = w;
+          ctl->item_nt0[slot] = w >= 0 ? it.nt0 : 0;
           ptx::mbar_arrive(&ctl->item_full[slot]);
           if (w < 0) break;
-          const Item it = decode_item<GEN>(a, w, n_pairs);
           if (it.n_max == 0) continue;
-          if (!ptx::mbar_wait(&ctl->q_empty, (qc & 1) ^ 1, abort_flag)) break;
-          ptx::mbar_arrive_expect_tx(&ctl->q_full, QT * TB);
-#pragma unroll
-          for (int t = 0; t < QT; ++t)
+          bool ok = true;
+          // a Q tile is loaded only if it has key tiles to walk; tile 0 goes first and, with the first K tile,
+          // ahead of tile 1: the issuer starts tile 0 of this item while tile 1 of the previous one still works
+          auto load_q = [&](int t, uint32_t& qc) {
+            if ((t == 0 ? it.nt0 : it.nt1) == 0) return true;
+            if (!ptx::mbar_wait(&ctl->q_empty[t], (qc & 1) ^ 1, abort_flag)) return false;
+            ptx::mbar_arrive_expect_tx(&ctl->q_full[t], TB);
 #pragma unroll
             for (int hf = 0; hf < HALVES; ++hf)
-              ptx::tma_load_4d(sQ + t * TB + hf * HALF_BYTES, &tmQ, &ctl->q_full, hf * 64, it.row0 + t * BM, it.h,
-                               it.b);
-          ++qc;
-          bool ok = true;
+              ptx::tma_load_4d(sQ + t * TB + hf * HALF_BYTES, &tmQ, &ctl->q_full[t], hf * 64, it.row0 + t * BM, it.h, it.b);
+            ++qc;
+            return true;
+          };
+          if (!(ok = load_q(0, qc0))) break;
           for (int j = 0; j < it.n_max; ++j, ++g) {
             const int st = g % NSTAGE;
             const uint32_t ph = (g / NSTAGE) & 1;
@@ -282,6 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int hf = 0; hf < HALVES; ++hf)
               ptx::tma_load_4d(sK + st * TB + hf * HALF_BYTES, &tmK, &ctl->k_full[st], hf * 64, j * BN, it.hk, it.b);
+            if (j == 0 && !(ok = load_q(1, qc1))) break;
             if (!(ok = ptx::mbar_wait(&ctl->v_empty[st], ph ^ 1, abort_flag))) break;
             ptx::mbar_arrive_expect_tx(&ctl->v_full[st], TB);
 #pragma unroll
@@ -318,8 +328,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
         uint32_t g0 = 0;        // ring position of the item's first key tile
         uint32_t c0 = 0, c1 = 0;  // softmax iterations completed per tile (p_full phases)
-        uint32_t qc = 0;        // items with work seen so far (q_full phase)
+        uint32_t qc0 = 0, qc1 = 0;  // items whose Q tile 0 / 1 was used so far (q_full phases)
         bool ok = true;
+        bool pre0 = false;      // the first QK of tile 0 of the coming item has been issued already
 
         auto wait_k = [&](uint32_t g) { return uwait(&ctl->k_full[g % NSTAGE], (g / NSTAGE) & 1); };
         auto issue_qk = [&](int t, uint32_t g) {
@@ -342,6 +353,21 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         };
 
+        // first QK of tile t of an item whose first key tile sits at ring position g
+        auto first_qk = [&](int t, uint32_t& qc, uint32_t g, int nt_t) {
+          if (!uwait(&ctl->q_full[t], qc & 1)) return false;
+          ++qc;
+          if (!wait_k(g)) return false;
+          ptx::tc_fence_after();
+          issue_qk(t, g);
+          if (leader && nt_t == 1) ptx::mma_commit(&ctl->q_empty[t]);  // the only QK of this tile
+          return true;
+        };
+        // non-blocking probe, the same answer in every lane
+        auto utest = [&](uint64_t* bar, uint32_t parity) {
+          return __all_sync(0xffffffffu, ptx::mbar_test(bar, parity)) != 0;
+        };
+
         for (uint32_t i = 0; ok; ++i) {
           const int slot = i & 1;
           if (!uwait(&ctl->item_full[slot], (i >> 1) & 1)) break;
@@ -354,15 +380,26 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int nt0 = it.nt0, nt1 = it.nt1, n_max = it.n_max;
           auto nt = [&](int t) { return t == 0 ? nt0 : nt1; };
 
-          if (!(ok = uwait(&ctl->q_full, qc & 1))) break;
-          ++qc;
-          if (!(ok = wait_k(g0))) break;
-          ptx::tc_fence_after();
-#pragma unroll
-          for (int t = 0; t < QT; ++t)
-            if (nt(t) > 0) issue_qk(t, g0);
+          if (nt0 > 0 && !pre0 && !(ok = first_qk(0, qc0, g0, nt0))) break;
+          pre0 = false;
+          if (nt1 > 0 && !(ok = first_qk(1, qc1, g0, nt1))) break;
           if (leader) ptx::mma_commit(&ctl->k_empty[g0 % NSTAGE]);
-          if (leader && n_max == 1) ptx::mma_commit(&ctl->q_empty);
+          // Tile 0 is done and tile 1 still has key tiles to walk (the causal diagonal): if the next item is
+          // known and its Q tile 0 and first K tile have landed, start its tile 0 now, so that warpgroup 0
+          // does not sit idle for tile 1's last iteration.  Nothing here blocks.  (S_0 is free: its last P has
+          // been consumed in issue order; O_0 is not written before warpgroup 0 delivers the next P, i.e.
+          // after its epilogue.)
+          auto try_pre0 = [&]() {
+            if (pre0 || nt0 == 0) return;
+            const int nslot = (i + 1) & 1;
+            if (!utest(&ctl->item_full[nslot], ((i + 1) >> 1) & 1)) return;
+            const int nt0n = ctl->item_nt0[nslot];
+            const uint32_t gn = g0 + n_max;
+            if (nt0n <= 0 || !utest(&ctl->q_full[0], qc0 & 1) || !utest(&ctl->k_full[gn % NSTAGE], (gn / NSTAGE) & 1))
+              return;
+            if (!(ok = first_qk(0, qc0, gn, nt0n))) return;
+            pre0 = true;
+          };
 
           for (int j = 0; j < n_max && ok; ++j) {
             const uint32_t g = g0 + j;
@@ -387,11 +424,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
               if (do_qk) {
                 issue_qk(t, g + 1);
-                if (leader && t == last_qk) {
-                  ptx::mma_commit(&ctl->k_empty[(g + 1) % NSTAGE]);
-                  if (j + 2 == n_max) ptx::mma_commit(&ctl->q_empty);  // last QK of the item
-                }
+                if (leader && j + 2 == nt(t)) ptx::mma_commit(&ctl->q_empty[t]);  // last QK of this tile: its Q may be replaced
+                if (leader && t == last_qk) ptx::mma_commit(&ctl->k_empty[(g + 1) % NSTAGE]);
               }
+            }
+            if constexpr (D == 64) {
+              if (ok && j >= nt0 - 1 && nt1 > nt0) try_pre0();
             }
           }
           g0 += n_max;
