@@ -431,9 +431,9 @@ __global__ void __launch_bounds__(kThreads, 1)
               if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, mo + 3 * a.mask.sl);
             }
           }
-          // (one exponential in four on the FMA pipe: the 16 compute warps saturate the MUFU units in this phase;
-          // two in four is slower again)
-          float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), ptx::ex2_fma(x1.y));
+          // (one exponential in eight on the FMA pipe: the 16 compute warps saturate the MUFU units in this phase;
+          // one in four is as fast within half a percent, three in eight and more are slower again)
+          float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), (i & 4) ? ptx::ex2_fma(x1.y) : ptx::ex2(x1.y));
           if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
             const int q = q0 + col + i + shift;
             if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
