@@ -73,3 +73,27 @@ def test_block_operators_and_prefill_replay_from_a_cuda_graph(oracle):
     wo, _ = oracle.fwd(yy, yy, yy, causal=True)
     want_z = forc.silu_mul(torch.from_numpy(wo).bfloat16().float().numpy().reshape(H * S, D))
     assert np.abs(to_np(z) - want_z).max() <= 4 * TOL_ABS_16BIT * max(1.0, np.abs(want_z).max())
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph(oracle):
+    # the backward's three kernels (delta pre-pass, tensor-core kernel, conversion) are chained by programmatic
+    # dependent launches: the capture keeps those edges, and a replay with new data gives the new gradients
+    from tinytorch_b200 import op
+    B, H, S, D = 1, 2, 256, 64
+    q, qn = make((B, H, S, D), torch.float16, 721)
+    k, kn = make((B, H, S, D), torch.float16, 722)
+    v, vn = make((B, H, S, D), torch.float16, 723)
+    do, _ = make((B, H, S, D), torch.float16, 724)
+
+    def step():
+        o, lse = op.sdpAttentionFwd(q, k, v, isCausal=True)
+        return op.sdpAttentionBwd(do, q, k, v, o, lse, isCausal=True)
+
+    g, (dq, dk, dv) = _capture(step)
+    do2, do2n = make((B, H, S, D), torch.float16, 725)
+    do.copy_(do2)
+    g.replay()
+    torch.cuda.synchronize()
+    wq, wk, wv = oracle.bwd(qn, kn, vn, do2n, causal=True)
+    for got, want in ((dq, wq), (dk, wk), (dv, wv)):
+        assert np.abs(to_np(got) - want).max() <= TOL_ABS_16BIT
