@@ -422,9 +422,12 @@ def run_ours(args, w, wname):
         return res
 
     main = measure(w, wname, args.steps, args.warmup, with_e2e=not args.no_e2e)
-    extra = None
+    extra, others = None, {}
     if wname == "prefill" and not args.no_decode:
         extra = measure(WORKLOADS["decode"], "decode", max(5, args.steps), max(3, args.warmup), with_e2e=False)
+        # the other configurations of the benchmark table, device-resident inputs only
+        others = {n: measure(WORKLOADS[n], n, max(5, args.steps), max(3, args.warmup), with_e2e=False)
+                  for n in ("gqa", "train")}
 
     if rank == 0:
         cpu = None
@@ -450,6 +453,10 @@ def run_ours(args, w, wname):
             line["decode"] = {"metric": "decode HBM GB/s", "value": extra["value"], "unit": "GB/s",
                               "ms_per_step": extra["ms_per_step"], "roofline": extra["roofline"],
                               "config": config_of(WORKLOADS["decode"], "decode"), "clocks": extra["clocks"]}
+        for n, r in others.items():
+            line[n] = {"metric": metric_name(WORKLOADS[n]), "value": r["value"], "unit": "TFLOP/s",
+                       "ms_per_step": r["ms_per_step"], "roofline": r["roofline"],
+                       "config": config_of(WORKLOADS[n], n), "clocks": r["clocks"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -701,7 +708,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="prefill", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
+    ap.add_argument("--no-decode", action="store_true", help="skip the secondary measurements (decode, GQA prefill, training step)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
