@@ -1,0 +1,103 @@
+"""Randomised shapes in bulk: several seconds of random (dtype, head dimension, grouping, lengths, alignment of the
+causal triangle, sequence lengths) per entry point, each case compared on the GPU with an fp32 composition of the same
+operator in torch (scores, mask, softmax, product; gradients by autograd).  The bit-level checks against the CPU oracle
+are in the other test files; this one is about coverage of tile counts, ragged edges and work-item boundaries."""
+import math
+import time
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SECONDS = 6.0
+
+
+def _reference(q, k, v, causal, lens):
+    B, Hq, L, D = q.shape
+    Hkv, S = k.shape[1], k.shape[2]
+    g = Hq // Hkv
+    kf, vf = k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1)
+    s = torch.einsum("bhld,bhsd->bhls", q.float(), kf) / math.sqrt(D)
+    i = torch.arange(L, device=q.device)[:, None]
+    j = torch.arange(S, device=q.device)[None, :]
+    keep = torch.ones(L, S, dtype=torch.bool, device=q.device)
+    if causal is True:
+        keep = j <= i
+    elif causal == "bottom-right":
+        keep = j <= i + (S - L)
+    keep = keep[None, None].expand(B, Hq, L, S).clone()
+    if lens is not None:
+        keep &= j[None, None] < lens.view(B, 1, 1, 1)
+    p = torch.nan_to_num(torch.softmax(s.masked_fill(~keep, float("-inf")), -1), nan=0.0)  # rows without keys: 0
+    return torch.einsum("bhls,bhsd->bhld", p, vf)
+
+
+def _prefill_case(rng):
+    dt = [torch.float16, torch.bfloat16][rng.integers(2)]
+    D = [64, 128][rng.integers(2)]
+    B, Hkv, g = int(rng.integers(1, 4)), int(rng.integers(1, 4)), int(rng.choice([1, 2, 4]))
+    L, S = int(rng.integers(1, 1100)), int(rng.integers(1, 1100))
+    causal = [False, True, "bottom-right"][rng.integers(3)]
+    if causal == "bottom-right" and L > S:
+        L = S
+    mk = lambda *s: torch.randn(s, device="cuda").to(dt)
+    q, k, v = mk(B, Hkv * g, L, D), mk(B, Hkv, S, D), mk(B, Hkv, S, D)
+    lens = None
+    if causal is False and rng.integers(3) == 0:
+        lens = torch.from_numpy(rng.integers(1, S + 1, size=B).astype(np.int32)).cuda()
+    return q, k, v, causal, lens
+
+
+def test_random_prefill_cases():
+    from tinytorch_b200 import op
+    rng = np.random.default_rng(11)
+    t_end, n = time.time() + SECONDS, 0
+    while time.time() < t_end:
+        q, k, v, causal, lens = _prefill_case(rng)
+        o, _ = op.sdpAttentionFwd(q, k, v, isCausal=causal, kvLens=lens)
+        err = (o.float() - _reference(q, k, v, causal, lens)).abs().max().item()
+        assert err <= 2e-2, (q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, err)
+        n += 1
+    assert n > 50
+
+
+def test_random_backward_cases():
+    from tinytorch_b200 import op
+    rng = np.random.default_rng(12)
+    t_end, n = time.time() + SECONDS, 0
+    while time.time() < t_end:
+        q, k, v, causal, lens = _prefill_case(rng)
+        qr, kr, vr = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+        want = _reference(qr, kr, vr, causal, lens)
+        do = torch.randn_like(want).to(q.dtype)
+        want.backward(do.float())
+        o, lse = op.sdpAttentionFwd(q, k, v, isCausal=causal, kvLens=lens)
+        dq, dk, dv = op.sdpAttentionBwd(do, q, k, v, o, lse, isCausal=causal, kvLens=lens)
+        for got, ref in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
+            scale = max(1.0, ref.abs().max().item())  # 16-bit rounding of a gradient grows with its size
+            err = (got.float() - ref).abs().max().item()
+            assert err <= 2e-2 * scale, (q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, err, scale)
+        n += 1
+    assert n > 50
+
+
+def test_random_decode_cases():
+    from tinytorch_b200 import op
+    rng = np.random.default_rng(13)
+    t_end, n = time.time() + SECONDS, 0
+    while time.time() < t_end:
+        dt = [torch.float16, torch.bfloat16][rng.integers(2)]
+        D = [64, 128][rng.integers(2)]
+        B, Hkv = int(rng.integers(1, 9)), int(rng.integers(1, 5))
+        g = int(rng.choice([1, 2, 3, 4, 6, 8, 16]))
+        cap = int(rng.integers(1, 5000))
+        mk = lambda *s: torch.randn(s, device="cuda").to(dt)
+        q, k, v = mk(B, Hkv * g, 1, D), mk(B, Hkv, cap, D), mk(B, Hkv, cap, D)
+        lens = torch.from_numpy(rng.integers(1, cap + 1, size=B).astype(np.int32)).cuda()
+        o, _ = op.sdpAttentionDecode(q, k, v, lens)
+        err = (o.float() - _reference(q, k, v, False, lens)).abs().max().item()
+        assert err <= 2e-2, (dt, D, B, Hkv, g, cap, lens, err)
+        n += 1
+    assert n > 50
