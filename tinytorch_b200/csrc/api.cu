@@ -335,6 +335,7 @@ int tt_attn_decode_static(const tt_attn_decode_params* p) {
   a.B = p->B, a.Hq = p->Hq, a.Hkv = p->Hkv, a.capacity = p->capacity;
   a.scale = p->scale;
   a.kv_lens = p->kv_lens;
+  a.status = p->status;
   decode_plan_for(p->dtype, p->D, p->B, p->Hq, p->Hkv, p->capacity, &a.nsplit, &a.chunk);
   const size_t need =
       tt_attn_workspace_bytes(TT_ATTN_KIND_DECODE, p->dtype, p->B, p->Hq, p->Hkv, 1, p->capacity, p->D);

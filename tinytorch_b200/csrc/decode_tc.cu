@@ -240,6 +240,10 @@ __global__ void __launch_bounds__(kThreads, OCC)
       if (!ok) break;
       cur = nxt;
     }
+    // A wait has expired: whatever a consumer still reads from the queue must be the end marker, not an old item.
+    if (!ok && lane == 0) {
+      for (int slot = 0; slot < NFIFO; ++slot) ctl->item[slot].n_tiles = -1;
+    }
   } else if (warp == kIssuerWarp) {
     // ---------------------------------------------------------------- issuer --
     if (lane == 0) {
@@ -347,8 +351,12 @@ __global__ void __launch_bounds__(kThreads, OCC)
     };
 
     // warpgroup 0 stays one descriptor ahead (it stages the next item's Q); warpgroup 1 reads them in step
+    // After an expired wait next_desc() no longer waits and may return an old item, and the threads of a
+    // warpgroup meet at named barriers inside an item: so the warpgroup votes after every fetch and leaves
+    // together, before it acts on a descriptor that some of its threads did not wait for.
     ItemDesc it = next_desc(0), nx;
     nx.n_tiles = -1;
+    if (ptx::named_barrier_or(1 + wg, kSoft, !ok)) it.n_tiles = -1;
     if (wg == 0 && it.n_tiles > 0) {
       uint4 qv[2];
       load_q(it, qv);
@@ -507,9 +515,9 @@ __global__ void __launch_bounds__(kThreads, OCC)
             const float wa = ma == -INFINITY ? 0.f : ptx::ex2(ma - mn), wb = mbv == -INFINITY ? 0.f : ptx::ex2(mbv - mn);
             const float lt = la * wa + lbv * wb;
             float oh = (wa > 0.f ? __uint_as_float(oa[h]) * wa : 0.f) + (wb > 0.f ? __uint_as_float(ob[h]) * wb : 0.f);
-            if (!ok) oh = 0.f;
             const int hq = h0 + h;
-            if (r < D && h < group) {  // D = 64: lanes 64-127 hold copies; heads beyond the group are padding
+            if (r < D && h < group && ok) {  // D = 64: lanes 64-127 hold copies; heads beyond the group are padding
+              // (nothing is stored after an expired wait: the status word reports it)
               if (a.nsplit == 1) {
                 const float inv = lt > 0.f ? 1.f / lt : 0.f;
                 reinterpret_cast<T*>(a.o)[it.b * a.os.b + hq * a.os.h + r] = from_f32<T>(oh * inv);
@@ -527,6 +535,7 @@ __global__ void __launch_bounds__(kThreads, OCC)
       ++merges;
       tiles += it.n_tiles;
       it = wg == 0 ? nx : next_desc(items + 1);
+      if (ptx::named_barrier_or(1 + wg, kSoft, !ok)) break;
     }
   }
 

@@ -50,27 +50,6 @@ constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the
 constexpr int kTmemCols = 512;
 constexpr int kItemConsumers = 1 + QT * BM;  // issuer thread + every softmax thread
 
-// Developer aid, compiled out by default: with -DTT_ATTN_PROFILE the first CTA
-// writes clock64() stamps per work item to the buffer passed as `status`
-// (int64 [2 warpgroups][32 items][8 slots]).
-#ifdef TT_ATTN_PROFILE
-#define TT_STAMP(slot)                                                              \
-  do {                                                                              \
-    if (prof && i < 32) prof[(t * 32 + i) * 8 + (slot)] = clock64();               \
-  } while (0)
-#define TT_FINE(slot)                                                                              \
-  do {                                                                                              \
-    if (prof && i == 3 && j < 64) prof[2 * 32 * 8 + (t * 64 + j) * 4 + (slot)] = clock64();        \
-  } while (0)
-#else
-#define TT_STAMP(slot) \
-  do {                 \
-  } while (0)
-#define TT_FINE(slot) \
-  do {                \
-  } while (0)
-#endif
-
 struct __align__(8) SmemCtl {
   uint64_t q_full[QT], q_empty[QT];  // per query tile: tile 0 of the next item is loaded while tile 1 still works
   uint64_t k_full[NSTAGE], k_empty[NSTAGE], v_full[NSTAGE], v_empty[NSTAGE];
@@ -251,7 +230,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Register budget: the softmax warpgroups hold a whole 128-column S row per
   // thread; the producer / issuer warpgroup needs little.
   if (warp >= 8) {
-    ptx::setmaxnreg_dec<72>();
+    // (D = 128: 224 + 224 + 56 registers per thread over the three warpgroups; D = 64, whose issuing loop
+    // carries the look-ahead at item boundaries: 216 + 216 + 72.  Both add up to the 168 x 384 registers
+    // the CTA was launched with, so the increase below can always be served.)
+    ptx::setmaxnreg_dec<D == 128 ? 56 : 72>();
     if (warp == 8) {
       // ---------------------------------------------------------- producer --
       if (lane == 0) {
@@ -439,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    ptx::setmaxnreg_inc<216>();
+    ptx::setmaxnreg_inc<D == 128 ? 224 : 216>();
     // ------------------------------------------------------------- softmax --
     const int t = warp >> 2;          // query tile of this warpgroup
     const int r_in = tid & (BM - 1);  // row within the tile = TMEM lane
@@ -456,16 +438,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t ec = 0;   // items with work completed (o_full phase)
     bool ok = true;
     uint32_t s[BN];
-#ifdef TT_ATTN_PROFILE
-    long long* prof = (blockIdx.x == 0 && r_in == 0 && a.status) ? reinterpret_cast<long long*>(a.status) : nullptr;
-#endif
 
     // The warpgroup meets at named barriers in the epilogue, so its threads must
     // leave the loop together: an expired wait is voted on (twice per item) and
     // then every thread of the warpgroup unwinds.
     for (uint32_t i = 0;; ++i) {
       const int slot = i & 1;
-      TT_STAMP(0);
       ok = ptx::mbar_wait(&ctl->item_full[slot], (i >> 1) & 1, abort_flag);
       if (ptx::named_barrier_or(1 + t, BM, !ok)) break;
       const int w = ctl->item[slot];
@@ -473,10 +451,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (w < 0) break;
       const Item it = decode_item<GEN>(a, w, n_pairs);
       const int n_t = t == 0 ? it.nt0 : it.nt1;
-      TT_STAMP(1);
-#ifdef TT_ATTN_PROFILE
-      if (prof && i < 32) prof[(t * 32 + i) * 8 + 7] = n_t;
-#endif
       const int tile_row0 = it.row0 + t * BM;
       const int row = tile_row0 + r_in;  // global query row of this thread
       const int kv_len = it.kv_len;
@@ -498,13 +472,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int j = 0; j < n_t && ok; ++j) {
         ok = ptx::mbar_wait(&ctl->s_full[t], (cnt + j) & 1, abort_flag);
         if (!ok) break;
-        if (j == 0) TT_STAMP(2);
-        TT_FINE(0);
         ptx::tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) ptx::tmem_ld32p(tS + cc * 32, s + cc * 32);
         ptx::tmem_wait_ld();
-        TT_FINE(1);
 
         const int col0 = j * BN;
         if constexpr (GEN) {
@@ -592,26 +563,21 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           need_max = true;
         }
-        TT_FINE(2);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(&ctl->p_full[t]);
-        TT_FINE(3);
       }
       cnt += n_t;
-      TT_STAMP(3);
 
       // epilogue: O / l -> global, LSE.  The issuer may already be computing the
       // next item's first S_t; its first PV waits for this warpgroup's next P.
       if (ok) ok = ptx::mbar_wait(&ctl->o_full[t], ec & 1, abort_flag);
       ++ec;
       if (ptx::named_barrier_or(1 + t, BM, !ok)) break;
-      TT_STAMP(4);
       ptx::tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < D / 32; ++cc) ptx::tmem_ld32p(tO + cc * 32, s + cc * 32);
       ptx::tmem_wait_ld();
-      TT_STAMP(5);
       const float l = l2.x + l2.y;
       const float inv = l > 0.f ? 1.f / l : 0.f;
       // O leaves through shared memory and TMA stores (coalesced; rows beyond Lq
@@ -640,7 +606,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (ok && row < a.Lq && lse_row) *lse_row = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
-      TT_STAMP(6);
     }
     if (r_in == 0) ptx::bulk_wait_all();
   }

@@ -15,13 +15,17 @@
  *     signature-identical to function::sdpAttention (src/Function/FuncNNLayer.h:298-302).
  *     Calls the fused path when it applies (CUDA tensors, D in {64,128}, no
  *     dropout, a mask that is absent or of a supported form) and otherwise forwards to the
- *     original composition.
+ *     original composition.  Setting TINYTORCH_FUSED_ATTENTION=0 in the environment sends every
+ *     call to the original composition (read once, at the first call): the switch for A/B runs.
  * Error convention: a non-zero status is logged with LOGE and then ASSERT(false)
  * fires, which is what every reference op does on failure (src/Utils/Macros.h:34-43).
  */
 #pragma once
 
+#include <atomic>
 #include <cmath>
+#include <cstdint>
+#include <cstdlib>
 #include <optional>
 
 #include "TinyTorch.h"
@@ -83,12 +87,33 @@ inline void setMask(P& p, const Tensor& mask, const Tensor& /*q*/) {
     p.mask_strides[3 - (mask.dim() - 1) + i] = mask.size(i) == 1 ? 0 : mask.stride(i);
 }
 
+// TINYTORCH_FUSED_ATTENTION=0 turns the fused path off for the whole process.
+inline bool fusedEnabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("TINYTORCH_FUSED_ATTENTION");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// Calls that took the fused path so far (for tests and A/B runs).
+inline std::atomic<long>& fusedCalls() {
+  static std::atomic<long> n{0};
+  return n;
+}
+
+// The kernels read 16-byte vectors and TMA tiles: a view whose storage offset breaks that
+// alignment goes to the original composition instead of failing in the library.
+inline bool aligned16(const Tensor& t) { return (reinterpret_cast<uintptr_t>(t.dataPtr<>()) & 15) == 0; }
+
 inline bool applicable(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float dropoutP) {
+  if (!fusedEnabled()) return false;
   if (!q.device().isCuda() || dropoutP > 0.f) return false;
   if (q.dim() == 4 && k.dim() == 4 && !maskApplicable(mask, q, k)) return false;
   if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4) return false;
   if (q.dtype() != k.dtype() || q.dtype() != v.dtype()) return false;
   if (q.dtype() != DType::Float32 && q.dtype() != DType::Float16 && q.dtype() != DType::BFloat16) return false;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v)) return false;
   const auto D = q.size(-1);
   return (D == 64 || D == 128) && k.size(-1) == D && v.size(-1) == D && q.size(1) % k.size(1) == 0;
 }
@@ -252,6 +277,7 @@ class FuncSDPAttentionFused : public Function<FuncSDPAttentionFused> {
                         bool isCausal, const Tensor& attnMask, float dropoutP, std::optional<float> scale) {
     ASSERT(!(isCausal && attnMask.defined()) && dropoutP == 0.f);  // as src/Function/FuncNNLayer.h:242
     const float s = scale.has_value() ? scale.value() : (1.f / std::sqrt(static_cast<float>(query.size(-1))));
+    fused_detail::fusedCalls()++;
     auto [o, lse] = op::sdpAttentionFwd(query, key, value, isCausal, s, Tensor{}, attnMask);
     if (ctx) {
       // savedInputs holds every Tensor argument in order: query, key, value, attnMask
@@ -272,7 +298,13 @@ class FuncSDPAttentionFused : public Function<FuncSDPAttentionFused> {
     const bool isCausal = ctx->popData().toBool();
     const float s = ctx->popData().toFloat();
     const Tensor mask = ctx->savedInputs.size() > 3 ? ctx->savedInputs[3] : Tensor{};
-    auto grads = op::sdpAttentionBwd(grad, query, key, value, o, lse, isCausal, s, Tensor{}, mask);
+    // an upstream gradient that arrives as a misaligned view is copied once
+    Tensor dO = grad;
+    if (!fused_detail::aligned16(grad)) {
+      dO = Tensor(grad.shape(), grad.options().noGrad());
+      dO.copy_(grad);
+    }
+    auto grads = op::sdpAttentionBwd(dO, query, key, value, o, lse, isCausal, s, Tensor{}, mask);
     if (query.requiresGrad()) query.addGrad(std::move(grads[0]));
     if (key.requiresGrad()) key.addGrad(std::move(grads[1]));
     if (value.requiresGrad()) value.addGrad(std::move(grads[2]));
