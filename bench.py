@@ -93,6 +93,7 @@ def fwd_bytes(w):
 # processes, so the figure reported for a full launch is this ratio times the launch's algorithmic bytes.
 NCU_TRAFFIC_RATIO = {
     "fwd_tc_kernel": (251.1 / 269.5, "profiles/fwd_tc_kernel_prefill_bf16_S4096_D128.md"),
+    "bwd_tc_kernel": (293.7 / 270.0, "profiles/bwd_tc_kernel_train_fp16_S2048_D64.md"),
     "decode_kernel": (1218.2 / 1213.0, "profiles/decode_kernel_bf16_cap8192_D128.md"),
     "decode_tc_kernel": (1271.9 / 1248.0, "profiles/decode_tc_kernel_bf16_gqa4_cap8192_D128.md"),
     "linear_tc_kernel": (88.3 / 100.7, "profiles/linear_tc_kernel_bf16_4096x4096x4096.md"),
@@ -110,7 +111,8 @@ def traffic_of(kernel, algorithmic_bytes):
 
 
 def nominal_peaks():
-    return dict(tflops=2250.0, gbs=7700.0)
+    """Datasheet figures: dense bf16 / fp16 tensor throughput and HBM3e bandwidth (the 8 TB/s quoted for the target)."""
+    return dict(tflops=2250.0, gbs=8000.0)
 
 
 def measured_peaks():
@@ -118,8 +120,10 @@ def measured_peaks():
     if os.path.exists(p):
         with open(p) as f:
             d = json.load(f)
-        return dict(tflops=float(d["bf16_tflops"]), gbs=float(d["hbm_gbs"]), source="measured (MEASURED_PEAKS.json, burst)")
-    return dict(tflops=1590.0, gbs=6650.0, source="fallback (earlier measurement on this pool)")
+        return dict(tflops=float(d["bf16_tflops"]), gbs=float(d["hbm_gbs"]),
+                    tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    source="measured (MEASURED_PEAKS.json, burst)")
+    return dict(tflops=1590.0, gbs=6650.0, tflops_sustained=1400.0, source="fallback (earlier measurement on this pool)")
 
 
 class ClockSampler:
@@ -269,6 +273,49 @@ def run_reference_arm(args, w, wname):
     print(json.dumps(line), flush=True)
 
 
+def gpu_reference(w):
+    """The reference's own CUDA composition of the same attention (cuBLAS batched gemm + its generic kernels,
+    src/Function/FuncNNLayer.h:231-266) on this GPU, through oracle/_ref/shim_driver (the unmodified reference
+    sources compiled with USE_CUDA).  Its large-row softmax launch needs B*H*L <= 65535 per call
+    (src/Operation/OpNNLayerCuda.cuh:375), so one chunk of (batch, head) slices is timed and the whole
+    configuration is that time x the number of chunks."""
+    drv = os.path.join(ROOT, "oracle", "_ref", "shim_driver")
+    if not os.path.exists(drv):
+        return {"unavailable": "oracle/_ref/shim_driver not built (needs the reference tree at build time)"}
+    per_chunk = max(1, 65535 // w["L"])
+    n_slices = w["B"] * w["Hq"]
+    n = min(per_chunk, n_slices)
+    rng = np.random.default_rng(77)
+    tmp = tempfile.mkdtemp()
+    try:
+        paths = []
+        for name, S in (("q", w["L"]), ("k", w["S"]), ("v", w["S"])):
+            pth = os.path.join(tmp, name + ".bin")
+            (rng.standard_normal((n, 1, S, w["D"]), dtype=np.float32) * np.float32(w["std"])).tofile(pth)
+            paths.append(pth)
+        cmd = [drv, "fwd", w["dtype"], str(n), "1", "1", str(w["L"]), str(w["S"]), str(w["D"]), "1" if w["causal"] else "0",
+               "ref", str(n), "0"] + paths + [os.path.join(tmp, "o.bin")]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+        ms = None
+        for tok in r.stdout.split():
+            if tok.startswith("ms="):
+                ms = float(tok[3:])
+        if r.returncode != 0 or ms is None:
+            return {"unavailable": "shim_driver failed: %s" % (r.stderr.strip()[-200:] or r.stdout.strip()[-200:])}
+        chunks = -(-n_slices // n)
+        unit = dict(w, B=n, Hq=1, Hkv=1)
+        return {"value": step_flops(unit) / (ms / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_chunk": ms,
+                "slices_per_chunk": n, "chunks": chunks, "extrapolated": True,
+                "ms_whole_config": ms * n_slices / n,
+                "what": "function::sdpAttention of the reference on CUDA tensors, %s" % w["dtype"]}
+    except Exception as e:  # a baseline must not take the benchmark down
+        return {"unavailable": "%s: %s" % (type(e).__name__, e)}
+    finally:
+        for f in os.listdir(tmp):
+            os.unlink(os.path.join(tmp, f))
+        os.rmdir(tmp)
+
+
 def metric_name(w):
     return "decode HBM GB/s" if w["kind"] == "decode" else "attention TFLOP/s (causal-adj)"
 
@@ -362,26 +409,49 @@ def run_ours(args, w, wname):
             sampler.start()
         sec = timed(fn, steps, warmup)
         clocks = sampler.stop() if rank == 0 else {}
+        sustained = None
         if rank == 0 and world == 1:
-            # The timed region is a few milliseconds, shorter than the sampler's period.  One untimed second of
-            # the same launches afterwards shows the clocks and throttle reasons this kernel settles at.
+            # The timed region is a few milliseconds, shorter than the sampler's period and than the time the
+            # board takes to settle under its power limit.  One more second of the same launches, back to back
+            # and timed with CUDA events, shows what the kernel sustains and the clocks it settles at.
             probe = ClockSampler(local)
             probe.start()
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n_probe = 0
             t_end = time.time() + 1.0
+            p0.record()
             while time.time() < t_end:
                 for _ in range(20):
                     fn()
-                torch.cuda.synchronize()
+                n_probe += 20
+                if n_probe % 200 == 0:
+                    torch.cuda.synchronize()  # bounds the launch queue; the device stays busy for a second
+            p1.record()
+            torch.cuda.synchronize()
+            probe_sec = p0.elapsed_time(p1) / 1e3
             clocks["sustained_probe"] = probe.stop()
+            sustained = {"steps": n_probe, "seconds": probe_sec, "clocks": clocks["sustained_probe"]}
         decode = wl["kind"] == "decode"
         div = 1e9 if decode else 1e12
         per_gpu = work * steps / sec / div
         res.update(value=per_gpu * world, ms_per_step=sec / steps * 1e3, clocks=clocks, launches=launches * steps,
                    per_gpu=per_gpu, work=work)
         peak = peaks["gbs"] if decode else peaks["tflops"]
+        if sustained:
+            sv = work * sustained["steps"] / sustained["seconds"] / div
+            speak = peak if decode else peaks["tflops_sustained"]
+            sustained.update(value=sv, unit="GB/s" if decode else "TFLOP/s", peak=speak, frac=sv / speak,
+                             peak_source="copy rate (MEASURED_PEAKS.json)" if decode
+                             else "bf16 matmul back to back for seconds (MEASURED_PEAKS.json, bf16_tflops_sustained)")
+            res["sustained"] = sustained
+        train = wl["kind"] == "fwdbwd"
+        # the kernel that takes most of the step's device time (profiles/launch_list_bench_default.md)
         kern = (("decode_tc_kernel" if wl["Hq"] != wl["Hkv"] else "decode_kernel") if decode
-                else ("fwd_simt_kernel" if wl["dtype"] == "f32" else "fwd_tc_kernel"))
-        alg_bytes = work if decode else (fwd_bytes(wl) if wl["kind"] == "fwd" else None)
+                else ("fwd_simt_kernel" if wl["dtype"] == "f32" else ("bwd_tc_kernel" if train else "fwd_tc_kernel")))
+        # algorithmic bytes of that kernel's launch (backward: Q, K, V, dO read, dK, dV and the fp32 dQ written)
+        alg_bytes = work if decode else (fwd_bytes(wl) if wl["kind"] == "fwd" else (
+            float((4 * wl["B"] * wl["Hq"] * wl["L"] * wl["D"] + 2 * wl["B"] * wl["Hkv"] * wl["S"] * wl["D"]) * ESIZE[wl["dtype"]]
+                  + 4 * wl["B"] * wl["Hq"] * wl["L"] * (wl["D"] + 2)) if wl["dtype"] != "f32" else None))
         traffic, traffic_src = traffic_of(kern, alg_bytes)
         nominal = nominal_peaks()["gbs" if decode else "tflops"]
         res["roofline"] = {"bound": "hbm" if decode else "tensor", "achieved": per_gpu, "peak": peak,
@@ -416,13 +486,77 @@ def run_ours(args, w, wname):
             sec2 = timed(e2e_step, es, 1)
             h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hdo) if train else (hq, hk, hv)))
             d2h = ho.numel() * ho.element_size() + (sum(t.numel() * t.element_size() for t in hg) if train else 0)
+            # What the host link alone allows: the same pinned buffers copied in and out, no kernel.  With N ranks
+            # on one host the copies of all ranks share its PCIe root ports and memory bandwidth.
+            dsts = [torch.empty_like(t, device=dev) for t in ((hq, hk, hv, hdo) if train else (hq, hk, hv))]
+            outs = ([ho] + hg) if train else [ho]
+            dos = [torch.empty_like(t, device=dev) for t in outs]
+            cp_in, cp_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            def copy_only():
+                cur = torch.cuda.current_stream(dev)
+                cp_in.wait_stream(cur), cp_out.wait_stream(cur)
+                with torch.cuda.stream(cp_in):
+                    for d_, h_ in zip(dsts, (hq, hk, hv, hdo) if train else (hq, hk, hv)):
+                        d_.copy_(h_, non_blocking=True)
+                with torch.cuda.stream(cp_out):
+                    for h_, d_ in zip(outs, dos):
+                        h_.copy_(d_, non_blocking=True)
+                cur.wait_stream(cp_in), cur.wait_stream(cp_out)
+            sec3 = timed(copy_only, es, 1)
             res["e2e"] = {"value": work * es / sec2 / div * world, "unit": "GB/s" if decode else "TFLOP/s",
                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                          "ms_per_step": sec2 / es * 1e3}
+                          "ms_per_step": sec2 / es * 1e3,
+                          "copy_only_ms_per_step": sec3 / es * 1e3,
+                          "host_link_gbs": (h2d + d2h) * world * es / sec3 / 1e9,
+                          "frac_of_copy_ceiling": sec3 / sec2}
         return res
+
+    def strong(wl, name, steps, warmup):
+        """The named configuration partitioned over the ranks: each rank holds only its contiguous range of
+        (batch, kv-head) units (tinytorch_b200.shard.unit_range), runs the same kernels on it, and the value is
+        the whole configuration's work over the slowest rank's time.  Then the optional all-gather of O."""
+        from tinytorch_b200 import shard
+        n_units = wl["B"] * wl["Hkv"]
+        u0, u1 = shard.unit_range(n_units, rank, world)
+        g = wl["Hq"] // wl["Hkv"]
+        sw = dict(wl, B=u1 - u0, Hq=g, Hkv=1)  # a unit is one kv head with its g query heads: a batch entry of its own
+        q, k, v = build_inputs(sw, 4321)
+        decode = wl["kind"] == "decode"
+        if decode:
+            # lengths belong to sequences; every unit of a sequence carries its sequence's length
+            lens_b = np.random.default_rng(1234).integers(1024, wl["S"] + 1, size=wl["B"]).astype(np.int32)
+            lens_u = np.repeat(lens_b, wl["Hkv"])[u0:u1].copy()
+            lens = torch.from_numpy(lens_u).to(dev)
+            fn = lambda: op.sdpAttentionDecode(q, k, v, lens)
+            total = decode_bytes(wl, lens_b)
+        else:
+            fn = lambda: op.sdpAttentionFwd(q, k, v, isCausal=wl["causal"])
+            total = step_flops(wl)
+        sec = timed(fn, steps, warmup)
+        # all-gather of the rank's O block on a side stream, handed over by events
+        # (reference: src/Distributed/BackendNCCL.cpp:49-62, src/Distributed/BackendNCCL.h:167-189)
+        o = fn()[0]
+        o_view = o.reshape(1, (u1 - u0) * g, wl["L"], wl["D"])
+        side = torch.cuda.Stream(dev)
+        def gather():
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                out = shard.all_gather_output(o_view, n_units, world, group_size=g)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            return out
+        gsec = timed(gather, 3, 1)
+        div = 1e9 if decode else 1e12
+        return {"value": total * steps / sec / div, "unit": "GB/s" if decode else "TFLOP/s",
+                "ms_per_step": sec / steps * 1e3, "units_per_rank": [n_units // world, -(-n_units // world)],
+                "allgather_ms": gsec / 3 * 1e3, "allgather_bytes": wl["B"] * wl["Hq"] * wl["L"] * wl["D"] * ESIZE[wl["dtype"]],
+                "scaling": "strong", "config": config_of(wl, name)}
 
     main = measure(w, wname, args.steps, args.warmup, with_e2e=not args.no_e2e)
     extra, others = None, {}
+    strong_keys = {}
+    if wname == "prefill" and world > 1 and not args.no_decode:
+        strong_keys["prefill"] = strong(w, wname, args.steps, args.warmup)
+        strong_keys["decode"] = strong(WORKLOADS["decode"], "decode", max(5, args.steps), max(3, args.warmup))
     if wname == "prefill" and not args.no_decode:
         extra = measure(WORKLOADS["decode"], "decode", max(5, args.steps), max(3, args.warmup), with_e2e=False)
         # the other configurations of the benchmark table, device-resident inputs only
@@ -449,14 +583,27 @@ def run_ours(args, w, wname):
             "e2e": main.get("e2e"), "gpu_launches": main["launches"], "roofline": main["roofline"],
             "cpu_baseline": cpu,
         }
-        if extra:
-            line["decode"] = {"metric": "decode HBM GB/s", "value": extra["value"], "unit": "GB/s",
-                              "ms_per_step": extra["ms_per_step"], "roofline": extra["roofline"],
-                              "config": config_of(WORKLOADS["decode"], "decode"), "clocks": extra["clocks"]}
+        if main.get("sustained"):
+            line["sustained"] = main["sustained"]
+        if world == 1 and wname == "prefill" and not args.no_decode and not args.no_cpu:
+            line["gpu_reference"] = gpu_reference(w)
         for n, r in others.items():
             line[n] = {"metric": metric_name(WORKLOADS[n]), "value": r["value"], "unit": "TFLOP/s",
                        "ms_per_step": r["ms_per_step"], "roofline": r["roofline"],
                        "config": config_of(WORKLOADS[n], n), "clocks": r["clocks"]}
+            if r.get("sustained"):
+                line[n]["sustained"] = r["sustained"]
+        if strong_keys:
+            line["strong"] = strong_keys
+        # last, so that a record that keeps only the end of the line keeps the decode figures
+        if extra:
+            line["decode"] = {"metric": "decode HBM GB/s", "value": extra["value"], "unit": "GB/s",
+                              "ms_per_step": extra["ms_per_step"], "roofline": extra["roofline"],
+                              "config": config_of(WORKLOADS["decode"], "decode"), "clocks": extra["clocks"]}
+            if extra.get("sustained"):
+                line["decode"]["sustained"] = extra["sustained"]
+            if strong_keys:
+                line["decode"]["strong_value"] = strong_keys["decode"]["value"]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

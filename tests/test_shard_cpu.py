@@ -62,3 +62,26 @@ def test_two_ranks_gather_equals_single(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), 3, str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["rank0.ok", "rank1.ok"]
+
+
+def _worker_empty(rank, world, port, out_dir):
+    # one unit over two ranks: rank 1 owns nothing and still takes part in the gather
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g, L, D = 2, 4, 8
+    full = torch.arange(g * L * D, dtype=torch.float32).view(1, g, L, D)
+    b0, b1 = shard.unit_range(1, rank, world)
+    local = full[:, b0 * g:b1 * g]
+    ok = True
+    for gs in (g, None):  # group size given / agreed on by the ranks
+        got = shard.all_gather_output(local, 1, world, group_size=gs)
+        ok = ok and torch.equal(got, full[0])
+    open(os.path.join(out_dir, "rank%d.%s" % (rank, "ok" if ok else "bad")), "w").close()
+    dist.destroy_process_group()
+
+
+def test_gather_with_a_rank_that_owns_no_unit(tmp_path):
+    world = 2
+    mp.spawn(_worker_empty, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["rank0.ok", "rank1.ok"]

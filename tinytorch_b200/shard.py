@@ -35,13 +35,23 @@ def shard_bh(t, n_kv_units, rank, world):
     return t.view(B * H, S, D)[b0 * g:b1 * g].unsqueeze(0)
 
 
-def all_gather_output(o_local, n_kv_units, world, group=None):
+def all_gather_output(o_local, n_kv_units, world, group=None, group_size=None):
     """Gather per-rank O shards ([1, units_r*g, L, D]) into [sum units*g, L, D].
 
-    Uses all_gather on equal-sized padded blocks when shard sizes differ.
+    Uses all_gather on equal-sized padded blocks when shard sizes differ.  `group_size` is g, the number of
+    query heads per kv head; when it is not given it is taken from the largest local shard over the ranks
+    (a rank without units cannot tell from its own, empty shard).
     """
     sizes = [unit_range(n_kv_units, r, world) for r in range(world)]
-    g = o_local.shape[1] // max(1, sizes[dist.get_rank(group)][1] - sizes[dist.get_rank(group)][0])
+    mine = sizes[dist.get_rank(group)]
+    if group_size is None:
+        units = mine[1] - mine[0]
+        gt = torch.tensor([o_local.shape[1] // units if units else 0], dtype=torch.int64, device=o_local.device)
+        dist.all_reduce(gt, op=dist.ReduceOp.MAX, group=group)
+        group_size = int(gt.item())
+    g = group_size
+    if o_local.shape[1] != (mine[1] - mine[0]) * g:
+        raise ValueError("local shard has %d rows of heads, expected %d" % (o_local.shape[1], (mine[1] - mine[0]) * g))
     mx = max(e - b for b, e in sizes) * g
     pad = torch.zeros((mx,) + tuple(o_local.shape[2:]), dtype=o_local.dtype, device=o_local.device)
     pad[:o_local.shape[1]] = o_local[0]
