@@ -281,6 +281,14 @@ TT_ATTN_API int tt_attn_decode_append(const tt_attn_decode_append_params* p);
 #define TT_ATTN_STATIC_SCRATCH_BYTES (24u << 20)
 TT_ATTN_API int tt_attn_decode_static(const tt_attn_decode_params* p);
 
+/* Self-test of the bounded device-side waits: launches one CTA that waits `limit_ns` nanoseconds
+ * (1 .. 2e9) on a barrier nothing arrives on.  The kernel returns by itself, ORs status bit 1
+ * (a wait expired) into *status (device memory, required) and, if `waited_ns` (device memory) is
+ * given, stores how long the wait lasted.  Enqueues on `stream` like every other entry point.
+ * For tests of a host's handling of the status word; it has no counterpart in the reference. */
+TT_ATTN_API int tt_attn_selftest_wait_expiry(int device, void* stream, uint64_t limit_ns, int32_t* status,
+                                             unsigned long long* waited_ns);
+
 /* Scratch bytes the given call needs (0 if none; the fp16/bf16 forward needs a
  * 256-byte block for its work counter).  Skv is the cache capacity
  * for TT_ATTN_KIND_DECODE. */

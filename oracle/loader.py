@@ -38,11 +38,15 @@ def _ptr(a):
     return a.ctypes.data_as(C.c_void_p) if a is not None else None
 
 
-def build(ref_root="/root/reference"):
-    """Compile both checkers with the Makefile beside this file."""
+def build(ref_root=None):
+    """Compile both checkers with the Makefile beside this file.  The reference tree is taken from
+    `ref_root`, else from $TT_REFERENCE_ROOT, else the Makefile looks for a directory named "reference"
+    beside this repository; without one only the plain-C oracle is built."""
     import subprocess
-    subprocess.run(["make", "-C", HERE, "-j8", "all", f"REF={ref_root}"], check=True,
-                   stdout=subprocess.DEVNULL)
+    cmd = ["make", "-C", HERE, "-j8", "all"]
+    if ref_root:
+        cmd.append(f"REF={ref_root}")
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
 
 
 class Oracle:

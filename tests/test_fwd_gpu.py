@@ -138,7 +138,8 @@ def test_config2_full_size_slices(oracle):
     o2, lse2 = _run(q, k, v, isCausal=True)
     assert torch.equal(o, o2) and torch.equal(lse, lse2)  # run-to-run determinism
     assert bool(torch.isfinite(o.float()).all())
-    for (b, h) in ((0, 0), (3, 31)):
+    # the first unit, the last one, and one from the middle of the grid (where a CTA changes heads mid-way)
+    for (b, h) in ((0, 0), (1, 19), (3, 31)):
         qn, kn, vn = (to_np(t[b:b + 1, h:h + 1]) for t in (q, k, v))
         wo, wl = oracle.fwd(qn, kn, vn, causal=True)
         assert np.abs(to_np(o[b:b + 1, h:h + 1]) - wo).max() <= TOL_ABS_16BIT
@@ -160,7 +161,7 @@ def test_config3_gqa_fp16_slices(oracle):
     k = (torch.randn((B, Hkv, S, D), generator=g, device="cuda") * 0.5).half()
     v = (torch.randn((B, Hkv, S, D), generator=g, device="cuda") * 0.5).half()
     o, lse = _run(q, k, v, isCausal=True)
-    for (b, hk) in ((0, 0), (7, 7)):
+    for (b, hk) in ((0, 0), (4, 3), (7, 7)):
         qn = to_np(q[b:b + 1, hk * 4:hk * 4 + 4])
         kn, vn = to_np(k[b:b + 1, hk:hk + 1]), to_np(v[b:b + 1, hk:hk + 1])
         wo, wl = oracle.fwd(qn, kn, vn, causal=True)

@@ -1,17 +1,20 @@
-"""Randomised shapes in bulk: several seconds of random (dtype, head dimension, grouping, lengths, alignment of the
-causal triangle, sequence lengths) per entry point, each case compared on the GPU with an fp32 composition of the same
-operator in torch (scores, mask, softmax, product; gradients by autograd).  The bit-level checks against the CPU oracle
-are in the other test files; this one is about coverage of tile counts, ragged edges and work-item boundaries."""
+"""Randomised shapes in bulk: a fixed number of seeded random cases (dtype, head dimension, grouping, lengths,
+alignment of the causal triangle, sequence lengths) per entry point, each compared on the GPU with an fp32 composition
+of the same operator in torch (scores, mask, softmax, product; gradients by autograd).  The bit-level checks against
+the CPU oracle are in the other test files; this one is about coverage of tile counts, ragged edges and work-item
+boundaries.  Shapes and data of case i depend only on (entry point's seed, i), so a failure is replayed from the
+numbers in its message."""
 import math
-import time
 
 import numpy as np
 import pytest
 import torch
 
+from gpu_util import ULP
+
 pytestmark = pytest.mark.gpu
 
-SECONDS = 6.0
+CASES = 150  # per entry point
 
 
 def _reference(q, k, v, causal, lens):
@@ -34,6 +37,12 @@ def _reference(q, k, v, causal, lens):
     return torch.einsum("bhls,bhsd->bhld", p, vf)
 
 
+def _rng(seed, i):
+    """numpy and torch generators of case i: independent of the cases before it."""
+    torch.manual_seed(seed * 100003 + i)
+    return np.random.default_rng([seed, i])
+
+
 def _prefill_case(rng):
     dt = [torch.float16, torch.bfloat16][rng.integers(2)]
     D = [64, 128][rng.integers(2)]
@@ -52,23 +61,18 @@ def _prefill_case(rng):
 
 def test_random_prefill_cases():
     from tinytorch_b200 import op
-    rng = np.random.default_rng(11)
-    t_end, n = time.time() + SECONDS, 0
-    while time.time() < t_end:
-        q, k, v, causal, lens = _prefill_case(rng)
+    for i in range(CASES):
+        q, k, v, causal, lens = _prefill_case(_rng(11, i))
         o, _ = op.sdpAttentionFwd(q, k, v, isCausal=causal, kvLens=lens)
         err = (o.float() - _reference(q, k, v, causal, lens)).abs().max().item()
-        assert err <= 2e-2, (q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, err)
-        n += 1
-    assert n > 50
+        assert err <= 2e-2, ("seed 11 case %d" % i, q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, err)
 
 
 def test_random_backward_cases():
     from tinytorch_b200 import op
-    rng = np.random.default_rng(12)
-    t_end, n = time.time() + SECONDS, 0
-    while time.time() < t_end:
-        q, k, v, causal, lens = _prefill_case(rng)
+    worst = 0.0
+    for i in range(CASES):
+        q, k, v, causal, lens = _prefill_case(_rng(12, i))
         qr, kr, vr = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
         want = _reference(qr, kr, vr, causal, lens)
         do = torch.randn_like(want).to(q.dtype)
@@ -76,18 +80,24 @@ def test_random_backward_cases():
         o, lse = op.sdpAttentionFwd(q, k, v, isCausal=causal, kvLens=lens)
         dq, dk, dv = op.sdpAttentionBwd(do, q, k, v, o, lse, isCausal=causal, kvLens=lens)
         for got, ref in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
-            scale = max(1.0, ref.abs().max().item())  # 16-bit rounding of a gradient grows with its size
-            err = (got.float() - ref).abs().max().item()
-            assert err <= 2e-2 * scale, (q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, err, scale)
-        n += 1
-    assert n > 50
+            # element-wise: 2e-2 absolute plus two units in the last place of the element's magnitude, plus a
+            # quarter unit of the tensor's largest element.  The last term is for long reductions that cancel:
+            # dK / dV sum one product per (query row, query head of the group), here up to a few thousand, whose
+            # operands (P, dS) are rounded to 16 bits; that error grows with the size of the terms, not with the
+            # size of the sum (seed 12 case 41: 1684 rows onto 7 keys, an element that sums to -0.002 in a tensor
+            # whose largest element is 21.8 is off by 0.029).  The oracle tests in test_bwd_gpu.py use the first
+            # two terms only.
+            bound = 2e-2 + 2.0 * ULP[q.dtype] * ref.abs() + 0.25 * ULP[q.dtype] * ref.abs().max()
+            ratio = ((got.float() - ref).abs() / bound).max().item()
+            worst = max(worst, ratio)
+            assert ratio <= 1.0, ("seed 12 case %d" % i, q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, ratio)
+    print("random backward cases: largest error / bound = %.3f" % worst)
 
 
 def test_random_decode_cases():
     from tinytorch_b200 import op
-    rng = np.random.default_rng(13)
-    t_end, n = time.time() + SECONDS, 0
-    while time.time() < t_end:
+    for i in range(CASES):
+        rng = _rng(13, i)
         dt = [torch.float16, torch.bfloat16][rng.integers(2)]
         D = [64, 128][rng.integers(2)]
         B, Hkv = int(rng.integers(1, 9)), int(rng.integers(1, 5))
@@ -98,6 +108,4 @@ def test_random_decode_cases():
         lens = torch.from_numpy(rng.integers(1, cap + 1, size=B).astype(np.int32)).cuda()
         o, _ = op.sdpAttentionDecode(q, k, v, lens)
         err = (o.float() - _reference(q, k, v, False, lens)).abs().max().item()
-        assert err <= 2e-2, (dt, D, B, Hkv, g, cap, lens, err)
-        n += 1
-    assert n > 50
+        assert err <= 2e-2, ("seed 13 case %d" % i, dt, D, B, Hkv, g, cap, lens, err)

@@ -6,7 +6,8 @@ per-split partial results live in a fixed array inside the library.  The test
 calls it directly through the C ABI, twice in a row with different inputs (the
 array keeps the first call's contents, which must not leak into the second), and
 compares each result with the regular tt_attn_decode entry point on the same
-inputs.  Collected last so that a failure here cannot mask any other test.
+inputs and with the CPU oracle, on every scan path the entry point can take.
+Collected last so that a failure here cannot mask any other test.
 """
 import ctypes as C
 
@@ -19,13 +20,13 @@ from gpu_util import TOL_ABS_16BIT, make
 pytestmark = pytest.mark.gpu
 
 
-def _params(q, k, v, o, lens, scale):
+def _params(q, k, v, o, lens, scale, status=None):
     from tinytorch_b200 import _capi
     B, Hq, _, D = q.shape
     _, Hkv, cap, _ = k.shape
     p = _capi.DecodeParams()
     p.struct_size = C.sizeof(_capi.DecodeParams)
-    p.dtype = _capi.BF16
+    p.dtype = {torch.bfloat16: _capi.BF16, torch.float16: _capi.F16, torch.float32: _capi.F32}[q.dtype]
     p.B, p.Hq, p.Hkv, p.capacity, p.D = B, Hq, Hkv, cap, D
     p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
     p.lse = None
@@ -35,30 +36,80 @@ def _params(q, k, v, o, lens, scale):
     p.kv_lens = lens.data_ptr()
     p.device = torch.cuda.current_device()
     p.stream = torch.cuda.current_stream().cuda_stream
-    p.workspace, p.workspace_bytes, p.alloc, p.status = None, 0, None, None
+    p.workspace, p.workspace_bytes, p.alloc = None, 0, None
+    p.status = status.data_ptr() if status is not None else None
     return p
 
 
-def test_static_scratch_matches_regular_decode_twice():
+# (query heads, kv heads, head dimension, dtype, cache capacity): the tensor-core scan (several query heads per
+# kv head), the CUDA-core scan with its combine kernel (one query head per kv head, cache split), fp16 at D = 64,
+# a cache short enough for a single split (no partials at all), and fp32
+CASES = [
+    (8, 2, 128, torch.bfloat16, 3000),
+    (4, 4, 128, torch.bfloat16, 3000),
+    (6, 2, 64, torch.float16, 2500),
+    (4, 4, 64, torch.float16, 400),
+    (2, 2, 128, torch.float32, 1500),
+]
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,dt,cap", CASES)
+def test_static_scratch_matches_regular_decode_twice(oracle, Hq, Hkv, D, dt, cap):
     from tinytorch_b200 import _capi, op
     lib = _capi.lib()
-    B, Hq, Hkv, cap, D = 4, 8, 2, 3000, 128   # 6 splits -> partials are in use
-    assert 0 < op.workspaceBytes(_capi.KIND_DECODE, torch.bfloat16, B, Hq, Hkv, 1, cap, D) <= _capi.STATIC_SCRATCH_BYTES
+    B = 4
+    assert op.workspaceBytes(_capi.KIND_DECODE, dt, B, Hq, Hkv, 1, cap, D) <= _capi.STATIC_SCRATCH_BYTES
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     for call, seed in enumerate((101, 202)):
-        q, _ = make((B, Hq, 1, D), torch.bfloat16, seed)
-        k, _ = make((B, Hkv, cap, D), torch.bfloat16, seed + 1)
-        v, _ = make((B, Hkv, cap, D), torch.bfloat16, seed + 2)
-        lens_np = np.array([cap, 1, 1777, 513] if call == 0 else [700, cap, 2, 2999], dtype=np.int32)
+        q, qn = make((B, Hq, 1, D), dt, seed)
+        k, kn = make((B, Hkv, cap, D), dt, seed + 1)
+        v, vn = make((B, Hkv, cap, D), dt, seed + 2)
+        lens_np = np.array([cap, 1, cap // 2 + 277, 513 % cap + 1] if call == 0 else [700 % cap + 1, cap, 2, cap - 1],
+                           dtype=np.int32)
         lens = torch.from_numpy(lens_np).cuda()
         want, _ = op.sdpAttentionDecode(q, k, v, lens, scale=0.09)
         got = torch.full_like(want, float("nan"))
-        p = _params(q, k, v, got, lens, 0.09)  # no workspace, no allocator hook
+        p = _params(q, k, v, got, lens, 0.09, status)  # no workspace, no allocator hook
         rc = lib.tt_attn_decode_static(C.byref(p))
         torch.cuda.synchronize()
         assert rc == 0, lib.tt_attn_strerror(rc)
+        assert int(status.item()) == 0  # the status word is passed on; no wait expired
         assert bool(torch.isfinite(got.float()).all())
-        assert float((got.float() - want.float()).abs().max()) <= TOL_ABS_16BIT
-        assert torch.equal(got, want)  # same kernels, same reduction order
+        assert torch.equal(got, want)  # same kernels, same reduction order as the regular entry point
+        # ... and both against the CPU oracle
+        wo, _ = oracle.fwd(qn, kn, vn, kv_lens=lens_np, scale=0.09)
+        if dt == torch.float32:
+            assert np.abs(got.cpu().numpy() - wo).max() <= 1e-5 * np.abs(wo).max()
+        else:
+            assert np.abs(got.float().cpu().numpy() - wo).max() <= TOL_ABS_16BIT
+
+
+def test_static_scratch_size_limit_both_sides():
+    # the largest batch whose partials still fit the array runs; one more is refused
+    from tinytorch_b200 import _capi, op
+    lib = _capi.lib()
+    Hq, Hkv = 16, 1   # many partial rows per byte of cache: the batch at the limit stays a few hundred MB
+    cap, D, dt = 8192, 128, torch.bfloat16
+    need = lambda B: op.workspaceBytes(_capi.KIND_DECODE, dt, B, Hq, Hkv, 1, cap, D)
+    lo, hi = 1, 1 << 16
+    while lo < hi:  # largest B with need(B) <= limit
+        mid = (lo + hi + 1) // 2
+        lo, hi = (mid, hi) if need(mid) <= _capi.STATIC_SCRATCH_BYTES else (lo, mid - 1)
+    B = lo
+    assert need(B) <= _capi.STATIC_SCRATCH_BYTES < need(B + 1)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for b, expect in ((B, 0), (B + 1, -10)):
+        q = torch.randn((b, Hq, 1, D), generator=g, device="cuda").to(dt)
+        k = torch.randn((b, Hkv, cap, D), generator=g, device="cuda").to(dt)
+        v = torch.randn((b, Hkv, cap, D), generator=g, device="cuda").to(dt)
+        lens = torch.full((b,), cap, dtype=torch.int32, device="cuda")
+        got = torch.zeros((b, Hq, 1, D), dtype=dt, device="cuda")
+        rc = lib.tt_attn_decode_static(C.byref(_params(q, k, v, got, lens, 0.09)))
+        torch.cuda.synchronize()
+        assert rc == expect, (b, rc)
+        if expect == 0:
+            want, _ = op.sdpAttentionDecode(q, k, v, lens, scale=0.09)
+            assert torch.equal(got, want)
 
 
 def test_static_scratch_rejects_oversize():

@@ -121,7 +121,8 @@ class LinearParams(C.Structure):
 
 FUSED_EXPORTS = ("tt_fused_add_rms_norm", "tt_silu_mul", "tt_linear")  # include/tt_fused.h
 
-EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_append", "tt_attn_decode_static", "tt_attn_workspace_bytes", "tt_attn_strerror",
+EXPORTS = ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_decode_append", "tt_attn_decode_static",
+           "tt_attn_selftest_wait_expiry", "tt_attn_workspace_bytes", "tt_attn_strerror",
            "tt_attn_last_cuda_error", "tt_attn_version")
 
 _lib = None
@@ -155,6 +156,8 @@ def lib():
         L.tt_linear.restype = C.c_int
         L.tt_attn_decode_static.argtypes = [C.POINTER(DecodeParams)]
         L.tt_attn_decode_static.restype = C.c_int
+        L.tt_attn_selftest_wait_expiry.argtypes = [C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
+        L.tt_attn_selftest_wait_expiry.restype = C.c_int
         for n in ("tt_attn_fwd", "tt_attn_bwd", "tt_attn_decode", "tt_attn_version"):
             getattr(L, n).restype = C.c_int
         L.tt_attn_workspace_bytes.argtypes = [C.c_int] * 8

@@ -349,6 +349,16 @@ int tt_attn_decode_static(const tt_attn_decode_params* p) {
   return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
 }
 
+int tt_attn_selftest_wait_expiry(int device, void* stream, uint64_t limit_ns, int32_t* status,
+                                 unsigned long long* waited_ns) {
+  if (!status) return TT_ATTN_ERR_NULL;
+  if (limit_ns == 0 || limit_ns > 2000000000ull) return TT_ATTN_ERR_SHAPE;  // the kernels' own limit is 2 s
+  DeviceGuard guard(device);
+  if (!guard.ok) return TT_ATTN_ERR_NO_DEVICE;
+  cudaError_t e = launch_wait_expiry(status, limit_ns, waited_ns, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? TT_ATTN_OK : launch_failed(e);
+}
+
 int tt_fused_add_rms_norm(const tt_fused_add_rms_norm_params* p) {
   if (!p) return TT_ATTN_ERR_NULL;
   if (p->struct_size != sizeof(tt_fused_add_rms_norm_params)) return TT_ATTN_ERR_STRUCT;

@@ -129,6 +129,9 @@ cudaError_t launch_silu_mul(int dtype, void* out, const void* x, int64_t rows, i
 cudaError_t launch_linear_tc(int dtype, const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                              int64_t ldx, int64_t ldw, int64_t ldy, int32_t* status, int device, cudaStream_t stream);
 
+// one CTA waiting `limit_ns` on an mbarrier nobody arrives on (selftest.cu)
+cudaError_t launch_wait_expiry(int32_t* status, uint64_t limit_ns, unsigned long long* waited_ns, cudaStream_t stream);
+
 // Split planning for decode, shared by the launcher and the workspace query.
 void decode_plan(int capacity, int* nsplit, int* chunk);
 // ... for the tensor-core path (several query heads per kv head): longer chunks, see decode.cu

@@ -72,7 +72,9 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  `abort_flag` (shared memory) lets one expired wait cut every
 // other wait of the CTA short.  Returns false if the wait was abandoned.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// `limit_ns` is the wall-clock limit of this wait.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_test(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -81,7 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }
