@@ -40,6 +40,27 @@ def test_linear_shapes(fused, dt, M, N, K, bias):
     _close(y, fused.linear(xn, wn, bn if bias else None))
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", [(2100, 4712, 200), (4096, 2560, 72), (2304, 4352, 1032)])
+def test_linear_tall_tiles(fused, dt, M, N, K):
+    # enough 256 x 256 tiles to fill the machine: the kernel takes 256-row tiles (two accumulators sharing a
+    # slice of w).  Ragged in every dimension; in the first shape the last tile's lower half lies wholly beyond M.
+    # The oracle runs on a band of rows from every part of the tile grid.
+    from tinytorch_b200 import fused as F
+    x, xn = make((M, K), DTYPES[dt], 631, std=0.5)
+    w, wn = make((N, K), DTYPES[dt], 632, std=0.5)
+    b, bn = make((N,), DTYPES[dt], 633)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = F._linear_raw(x, w, b, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    rows = sorted(set([0, 1, 127, 128, 129, 255, 256, 257, 383, 384, M // 2, M // 2 + 131, M - 130, M - 129, M - 2, M - 1]))
+    _close(y[rows], fused.linear(xn[rows], wn, bn))
+    # and the whole result against an fp32 product on the GPU
+    want = x.float() @ w.float().t() + b.float()
+    assert float((y.float() - want).abs().max()) <= TOL_ABS_16BIT * max(1.0, float(want.abs().max()))
+
+
 def test_golden_fixture(fused):
     from tinytorch_b200 import fused as F
     g = np.load(os.path.join(GOLDEN, "ref_seeded_linear.npz"))

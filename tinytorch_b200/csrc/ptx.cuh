@@ -51,21 +51,6 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Non-blocking probe (test_wait never suspends the thread; try_wait may, for a time the hardware chooses).
-__device__ __forceinline__ bool mbar_probe(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Wall-clock limit of any single wait.  A healthy kernel never waits longer
 // than a few milliseconds on one barrier; two seconds means a lost signal.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
@@ -84,26 +69,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (now - t0 > limit_ns) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
-// Bounded wait that polls with test_wait instead of try_wait.  A try_wait on a phase that is already
-// complete costs an MMA-issuing warp about 50 cycles next to busy warps, a test_wait about 15, and the
-// tensor pipe queues only two or three MMAs: for the waits between two batches of MMAs the difference
-// is tensor-pipe idle time.  (Polling burns issue slots, so long waits stay on mbar_wait.)
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_probe(bar, parity)) return true;
-    if ((it & 0x3ff) == 0) {
-      if (*abort_flag) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
         *abort_flag = 1;
         return false;
       }
@@ -436,21 +401,6 @@ __device__ __forceinline__ float ex2_fma(float x) {
   const float p = fmaf(fmaf(fmaf(0.055171750485897064f, f, 0.24261131882667542f), f, 0.6932609677314758f), f,
                        0.9999280571937561f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
-}
-
-// The same for a pair, on packed fp32 instructions: about five issue slots per element against nine.
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 xr = add2(x, make_float2(12582912.f, 12582912.f));
-  const float2 n = add2(xr, make_float2(-12582912.f, -12582912.f));
-  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = fma2(make_float2(0.055171750485897064f, 0.055171750485897064f), f,
-                  make_float2(0.24261131882667542f, 0.24261131882667542f));
-  p = fma2(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
-  p = fma2(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
-  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(xr.x) << 23)),
-                     __int_as_float(__float_as_int(p.y) + (__float_as_int(xr.y) << 23)));
 }
 
 }  // namespace ptx
