@@ -92,11 +92,11 @@ def fwd_bytes(w):
 # launch, from one ncu capture of a reduced case of each kernel; traffic grows in proportion to the units a launch
 # processes, so the figure reported for a full launch is this ratio times the launch's algorithmic bytes.
 NCU_TRAFFIC_RATIO = {
-    "fwd_tc_kernel": (251.1 / 269.5, "profiles/fwd_tc_kernel_prefill_bf16_S4096_D128.md"),
+    "fwd_tc_kernel": (254.3 / 269.5, "profiles/fwd_tc_kernel_prefill_bf16_S4096_D128.md"),
     "bwd_tc_kernel": (293.7 / 270.0, "profiles/bwd_tc_kernel_train_fp16_S2048_D64.md"),
     "decode_kernel": (1218.2 / 1213.0, "profiles/decode_kernel_bf16_cap8192_D128.md"),
     "decode_tc_kernel": (1271.9 / 1248.0, "profiles/decode_tc_kernel_bf16_gqa4_cap8192_D128.md"),
-    "linear_tc_kernel": (88.3 / 100.7, "profiles/linear_tc_kernel_bf16_4096x4096x4096.md"),
+    "linear_tc_kernel": (87.4 / 100.7, "profiles/linear_tc_kernel_bf16_4096x4096x4096.md"),
     "add_rms_norm_kernel": (478.5 / 536.9, "profiles/add_rms_norm_kernel_bf16_8192x8192.md"),
     "silu_mul_kernel": (309.3 / 352.3, "profiles/silu_mul_rows_kernel_bf16_4096x28672.md"),
 }
@@ -342,7 +342,7 @@ def run_ours(args, w, wname):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[w["dtype"]]
+    TDT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
     peaks = measured_peaks()
 
     def barrier():
@@ -370,13 +370,14 @@ def run_ours(args, w, wname):
 
     def build_inputs(wl, seed):
         g = torch.Generator(device=dev).manual_seed(seed + rank)
-        mk = lambda *s: (torch.randn(s, generator=g, device=dev) * wl["std"]).to(tdt)
+        mk = lambda *s: (torch.randn(s, generator=g, device=dev) * wl["std"]).to(TDT[wl["dtype"]])
         q = mk(wl["B"], wl["Hq"], wl["L"], wl["D"])
         k = mk(wl["B"], wl["Hkv"], wl["S"], wl["D"])
         v = mk(wl["B"], wl["Hkv"], wl["S"], wl["D"])
         return q, k, v
 
     def measure(wl, name, steps, warmup, with_e2e):
+        tdt = TDT[wl["dtype"]]  # each configuration in its own dtype
         q, k, v = build_inputs(wl, 1234)
         res = {}
         if wl["kind"] == "decode":

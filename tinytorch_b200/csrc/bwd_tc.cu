@@ -73,20 +73,6 @@ struct Cfg {
   static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
 };
 
-// Developer aid, compiled out by default: with -DTT_ATTN_PROFILE the first CTA
-// writes clock64() stamps per step to the buffer passed as `status`
-// (int64 [3 = warpgroup 0, warpgroup 1, issuer][32 steps][8 slots]).
-#ifdef TT_ATTN_PROFILE
-#define TT_BSTAMP(who, slot)                                                        \
-  do {                                                                              \
-    if (prof && n < 32) prof[((who)*32 + n) * 8 + (slot)] = clock64();             \
-  } while (0)
-#else
-#define TT_BSTAMP(who, slot) \
-  do {                       \
-  } while (0)
-#endif
-
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (BF16) {
@@ -177,12 +163,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-#ifdef TT_ATTN_PROFILE
-  long long* prof = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 17) &&
-                     a.status)
-                        ? reinterpret_cast<long long*>(a.status)
-                        : nullptr;
-#endif
   const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w) -> dQ (D = 128)
   const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
   const uint32_t tdV = tmem + 256;       // D columns
@@ -392,14 +372,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       float ln = -INFINITY, dn = 0.f;
       if (wg == 0 && n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
       // all threads reach this point every step, expired waits included
-      TT_BSTAMP(wg, 0);
       // This step's vectors are in shared memory.  (An mbarrier, not a barrier over the four warpgroups: the two
       // that drain dQ take longer per step, and the others may go on into the next step's exponentials meanwhile.
       // Warpgroup 0 cannot overwrite a buffer that is still read: it writes buffer n & 1 again after the first
       // MMAs of step n + 1 have completed, which every warpgroup's results of step n precede.)
       if (ok) ok = ptx::mbar_wait(&ctl->vec_full[n & 1], (n >> 1) & 1, abort_flag);
       if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
-      TT_BSTAMP(wg, 2);
       ptx::tc_fence_after();
       const bool diag = a.causal && q0 + shift < kv0 + BM;  // some (query, key) pairs of this step are masked
       const bool masked = diag || kv0 + BM > kv_len;
@@ -471,12 +449,10 @@ __global__ void __launch_bounds__(kThreads, 1)
               make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
         }
       }
-      TT_BSTAMP(wg, 3);
       ptx::tmem_wait_st();
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&ctl->pds_full);
-      TT_BSTAMP(wg, 4);
       if (wg == 0 && n + 1 < n_steps) {
         store_vec(n + 1, ln, dn);
         ptx::mbar_arrive(&ctl->vec_full[(n + 1) & 1]);
@@ -487,7 +463,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       } else {
         read_out_dq(n);
       }
-      TT_BSTAMP(wg, 6);
     }
     if (kPipe && n_steps > 0 && wg < 2) read_out_dq(n_steps - 1);
     if (r == 0) ptx::bulk_wait_all();
