@@ -15,7 +15,18 @@
 //       offset       : q is made a view that starts <offset> elements into a larger storage
 //   shim_driver fwdbwd <dtype> <N> <Hq> <Hkv> <L> <S> <D> <causal> <reps> <needq> <needk> <needv> q k v do out dq dk dv
 //       <reps> times: y = sdpAttentionFused(q, k, v); y.backward(dO)   (gradients accumulate on the leaves)
+//   shim_driver decode <dtype> <N> <Hq> <Hkv> <S> <D> <impl> lens q k v out
+//       impl = fused : op::sdpAttentionDecode through the dispatch table (one query per sequence against a cache
+//                      of capacity S with per-sequence lengths, a float32 file of N values)
+//       impl = ref   : what a TinyTorch caller writes without it: function::sdpAttention with a Bool mask
+//                      [N,1,1,S] built from the lengths (K / V repeated for grouped-query shapes)
+//   shim_driver fusedops <dtype> <rows> <dim> <nout>
+//       the block operators either side of attention (tinytorch_b200/shim/TinyTorchFusedOps.h): op::siluMul,
+//       op::fusedAddRmsNorm and function::linear's product are first computed by the reference's own CUDA
+//       implementations, then registerFusedOpsB200() replaces the dispatch-table entries and the same calls run
+//       again; prints the largest absolute differences (silu= rms_input= rms_residual= linear=)
 // Each run prints one line: fused_calls=<n> ms=<device time of the timed call(s)>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -24,6 +35,8 @@
 
 #include "TinyTorch.h"
 #include "TinyTorchFusedAttention.h"
+#include "TinyTorchFusedOps.h"
+#include "Utils/RandomGenerator.h"
 
 using namespace tinytorch;
 
@@ -46,6 +59,23 @@ static void writef(const char* path, const Tensor& t) {
     exit(2);
   }
   fclose(f);
+}
+
+static float maxAbsDiff(const Tensor& a, const Tensor& b) {
+  std::vector<float> x = a.to(DType::Float32).to(Device(DeviceType::CPU)).toList<float>();
+  std::vector<float> y = b.to(DType::Float32).to(Device(DeviceType::CPU)).toList<float>();
+  float m = x.size() == y.size() ? 0.f : 1e30f;
+  for (size_t i = 0; i < x.size() && i < y.size(); i++) {
+    const float d = std::fabs(x[i] - y[i]);
+    if (!(d <= m)) m = d;  // NaN propagates
+  }
+  return m;
+}
+
+static Tensor copyOf(const Tensor& t) {
+  Tensor c(t.shape(), t.options().noGrad());
+  c.copy_(t);
+  return c;
 }
 
 static DType parseDType(const char* s) {
@@ -149,6 +179,67 @@ int main(int argc, char** argv) {
         writef(argv[19 + i], Tensor::zeros(leaves[i]->shape()));
       }
     }
+  } else if (cmd == "fusedops" && argc == 6) {
+    const DType dt = parseDType(argv[2]);
+    const int64_t rows = atoll(argv[3]), dim = atoll(argv[4]), nout = atoll(argv[5]);
+    NoGradGuard guard;
+    const Device dev(DeviceType::CUDA, 0);
+    manualSeed(1234);
+    Tensor x = Tensor::randn({rows, 2 * dim}, options::device(dev)).to(dt);
+    Tensor h = Tensor::randn({rows, dim}, options::device(dev)).to(dt);
+    Tensor res = Tensor::randn({rows, dim}, options::device(dev)).to(dt);
+    Tensor w = Tensor::randn({dim}, options::device(dev)).to(dt);
+    Tensor lw = (Tensor::randn({nout, dim}, options::device(dev)) * 0.05f).to(dt);
+    Tensor lb = Tensor::randn({nout}, options::device(dev)).to(dt);
+    // the reference's own CUDA implementations
+    Tensor silu0 = op::siluMul(x);
+    Tensor h0 = copyOf(h), res0 = copyOf(res);
+    op::fusedAddRmsNorm(h0, res0, w, 1e-5f);
+    Tensor lin0 = op::matmul(h, lw, false, true, lb);
+    // the B200 kernels behind the same dispatch-table entries
+    op::registerFusedOpsB200();
+    Tensor silu1 = op::siluMul(x);
+    Tensor h1 = copyOf(h), res1 = copyOf(res);
+    op::fusedAddRmsNorm(h1, res1, w, 1e-5f);
+    Tensor lin1 = op::linearOpB200(h, lw, lb);
+    // (linearOpB200 declines what its kernel does not cover, fp32 for one, by returning an undefined tensor: -1)
+    printf("silu=%g rms_input=%g rms_residual=%g linear=%g ", maxAbsDiff(silu0, silu1), maxAbsDiff(h0, h1),
+           maxAbsDiff(res0, res1), lin1.defined() ? maxAbsDiff(lin0, lin1) : -1.f);
+  } else if (cmd == "decode" && argc == 14) {
+    const DType dt = parseDType(argv[2]);
+    const int64_t N = atoll(argv[3]), Hq = atoll(argv[4]), Hkv = atoll(argv[5]), S = atoll(argv[6]), D = atoll(argv[7]);
+    const std::string impl = argv[8];
+    NoGradGuard guard;
+    std::vector<float> lensf = readf(argv[9], static_cast<size_t>(N));
+    Tensor q = upload(argv[10], {N, Hq, 1, D}, dt, false);
+    Tensor k = upload(argv[11], {N, Hkv, S, D}, dt, false);
+    Tensor v = upload(argv[12], {N, Hkv, S, D}, dt, false);
+    auto stream = cuda::getCurrentCUDAStream(0).stream();
+    Tensor out;
+    if (impl == "fused") {
+      std::vector<int32_t> li(lensf.begin(), lensf.end());
+      Tensor lens = Tensor(li, IntArrayView({N}), options::dtype(DType::Int32)).to(Device(DeviceType::CUDA, 0));
+      const float scale = 1.f / std::sqrt(static_cast<float>(D));
+      out = op::sdpAttentionDecode(q, k, v, lens, scale);  // warm-up
+      cudaEventRecord(e0, stream);
+      out = op::sdpAttentionDecode(q, k, v, lens, scale);
+      cudaEventRecord(e1, stream);
+    } else {
+      std::vector<uint8_t> m(static_cast<size_t>(N * S));
+      for (int64_t b = 0; b < N; b++)
+        for (int64_t j = 0; j < S; j++) m[b * S + j] = j < static_cast<int64_t>(lensf[b]) ? 1 : 0;
+      Tensor mask = Tensor(m, IntArrayView({N, 1, 1, S}), options::dtype(DType::Bool)).to(Device(DeviceType::CUDA, 0));
+      const int64_t g = Hq / Hkv;
+      Tensor kk = g > 1 ? function::repeatInterleave(k, g, 1) : k;
+      Tensor vv = g > 1 ? function::repeatInterleave(v, g, 1) : v;
+      out = function::sdpAttention(q, kk, vv, false, mask);  // warm-up
+      cudaEventRecord(e0, stream);
+      out = function::sdpAttention(q, kk, vv, false, mask);
+      cudaEventRecord(e1, stream);
+    }
+    cudaEventSynchronize(e1);
+    cudaEventElapsedTime(&ms, e0, e1);
+    writef(argv[13], out);
   } else {
     fprintf(stderr, "usage: see the header of tests/cxx/shim_driver.cpp\n");
     return 2;

@@ -140,3 +140,53 @@ def test_fused_kernels_against_the_reference_cuda_composition(driver, tmp_path, 
     err = float(np.abs(got - ref).max())
     print("fused vs reference CUDA composition, %s L=%d D=%d: max abs diff %.3e" % (dtype, L, D, err))
     assert err <= 2e-2
+
+
+@pytest.mark.parametrize("N,Hq,Hkv,S,D,dtype", [(4, 8, 8, 8192, 128, "bf16"), (3, 8, 2, 3000, 64, "f16")])
+def test_decode_op_against_the_reference_mask_composition(driver, oracle, tmp_path, N, Hq, Hkv, S, D, dtype):
+    # config 4's shape on a few sequences: op::sdpAttentionDecode through the dispatch table against what a
+    # TinyTorch caller writes without it (sdpAttention with a Bool length mask, the reference's own CUDA kernels),
+    # and both against the CPU oracle
+    rng = np.random.default_rng(8)
+    q = _round(rng.standard_normal((N, Hq, 1, D)).astype(np.float32), dtype)
+    k = _round(rng.standard_normal((N, Hkv, S, D)).astype(np.float32), dtype)
+    v = _round(rng.standard_normal((N, Hkv, S, D)).astype(np.float32), dtype)
+    lens = rng.integers(S // 8, S + 1, size=N).astype(np.int32)
+    lens[0] = S
+    files = [_save(tmp_path, n, a) for n, a in (("lens.bin", lens.astype(np.float32)), ("q.bin", q), ("k.bin", k), ("v.bin", v))]
+    res = {}
+    for impl in ("fused", "ref"):
+        out = os.path.join(str(tmp_path), impl + ".bin")
+        driver(["decode", dtype, N, Hq, Hkv, S, D, impl] + files + [out])
+        res[impl] = _load(tmp_path, impl + ".bin", q.shape)
+    want, _ = oracle.fwd(q, k, v, kv_lens=lens)
+    print("decode %s: fused vs oracle %.3e, reference composition vs oracle %.3e" % (
+        dtype, float(np.abs(res["fused"] - want).max()), float(np.abs(res["ref"] - want).max())))
+    assert np.abs(res["fused"] - want).max() <= 2e-2
+    assert np.abs(res["fused"] - res["ref"]).max() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype,rows,dim,nout", [("bf16", 300, 1024, 512), ("f16", 64, 4096, 256), ("f32", 33, 200, 0)])
+def test_block_operators_replace_the_reference_cuda_entries(dtype, rows, dim, nout):
+    # tinytorch_b200/shim/TinyTorchFusedOps.h: after registerFusedOpsB200() the same op::siluMul /
+    # op::fusedAddRmsNorm calls reach the B200 kernels; the projection through linearOpB200.  Each against the
+    # reference's own CUDA implementation of the same operator on the same tensors (both compute in fp32 and
+    # round once, so they differ by at most a unit or two in the last place of the 16-bit result).
+    if not os.path.exists(DRIVER):
+        pytest.skip("oracle/_ref/shim_driver not built")
+    if dtype == "f32":
+        nout = 8
+    r = subprocess.run([DRIVER, "fusedops", dtype, str(rows), str(dim), str(nout)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr[-1000:])
+    d = {k: float(v) for k, v in re.findall(r"(\w+)=(-?[0-9.eE+-]+|nan|inf)", r.stdout)}
+    print(r.stdout.strip())
+    ulp = {"bf16": 2.0 ** -7, "f16": 2.0 ** -10, "f32": 2.0 ** -23}[dtype]
+    assert d["silu"] <= 2 * ulp * 8            # |silu(gate) * up| stays below ~8 for N(0,1) inputs
+    assert d["rms_residual"] <= 2 * ulp * 8
+    assert d["rms_input"] <= 2 * ulp * 16
+    if dtype == "f32":
+        assert d["linear"] == -1.0             # linearOpB200 declines fp32: the caller falls back to op::matmul
+    else:
+        # cuBLAS and the tensor-core kernel sum in different orders; outputs reach |y| ~ 8, where one unit in the
+        # last place of bf16 is 0.03
+        assert d["linear"] <= 2e-2 + 2 * ulp * 8

@@ -114,7 +114,25 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // key tiles near the start see the most query tiles under the causal mask: launch them first
-  const int nt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // CTAs start in the order of the linear block index.  Heads in order, and within a head the key tiles in
+  // order: under the causal mask the first key tile is seen by every query tile and walks longest.  Only the
+  // last `tail_heads` heads are ordered differently, key tile by key tile ACROSS those heads, so that the CTAs
+  // started last are the short ones and the grid ends together (in head order the last head's first key tile,
+  // the longest walk there is, would start when most SMs are nearly done).
+  const int n_kt = (a.Skv + BM - 1) / BM, n_heads = a.Hkv * a.B;
+  int nt, bh;
+  {
+    const int w = blockIdx.x, w0 = (n_heads - a.tail_heads) * n_kt;
+    if (w < w0) {
+      bh = w / n_kt;
+      nt = w - bh * n_kt;
+    } else {
+      const int x = w - w0;
+      nt = x / a.tail_heads;
+      bh = n_heads - a.tail_heads + (x - nt * a.tail_heads);
+    }
+  }
+  const int b = bh / a.Hkv, hk = bh - b * a.Hkv;
   const int group = a.Hq / a.Hkv;
   const int kv0 = nt * BM;
   int kv_len = a.Skv;
@@ -546,7 +564,18 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   auto kern = bwd_tc_kernel<D, BF16, GEN>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
   if (e != cudaSuccess) return e;
-  dim3 grid((a.Skv + BM - 1) / BM, a.Hkv, a.B);
+  const int n_kt = (a.Skv + BM - 1) / BM;
+  const long long n_ctas = static_cast<long long>(n_kt) * a.Hkv * a.B;
+  if (n_ctas > 0x7fffffffll) return cudaErrorInvalidValue;
+  dim3 grid(static_cast<unsigned>(n_ctas));
+  BwdArgs ka = a;
+  // two waves' worth of heads at the end of the grid (one CTA per SM); only worth it where walks differ in length
+  ka.tail_heads = 0;
+  if (a.causal) {
+    const long long heads = static_cast<long long>(a.Hkv) * a.B;
+    const long long want = (2ll * sm_count(device) + n_kt - 1) / n_kt;
+    ka.tail_heads = static_cast<int>(want < heads ? want : heads);
+  }
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -556,7 +585,7 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   cfg.dynamicSmemBytes = Cfg<D>::kSmem;
   cfg.stream = stream;
   cfg.attrs = attr, cfg.numAttrs = 1;  // early launch behind the delta pre-pass
-  e = cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tdo, tdq, a);
+  e = cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tdo, tdq, ka);
   if (e != cudaSuccess || !a.dq) return e;
   const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
   const int blocks = static_cast<int>((total + 255) / 256 < 8 * sm_count(device) ? (total + 255) / 256 : 8 * sm_count(device));

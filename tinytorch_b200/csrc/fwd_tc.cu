@@ -49,6 +49,10 @@ constexpr int NSTAGE = 2;    // K/V ring depth
 constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the producer and issuer warps
 constexpr int kTmemCols = 512;
 constexpr int kItemConsumers = 1 + QT * BM;  // issuer thread + every softmax thread
+#ifndef TT_FWD_TAIL_WAVES
+#define TT_FWD_TAIL_WAVES 2
+#endif
+constexpr int kTailWaves = TT_FWD_TAIL_WAVES;  // waves of work items at the end that are ordered longest first across heads
 
 struct __align__(8) SmemCtl {
   uint64_t q_full[QT], q_empty[QT];  // per query tile: tile 0 of the next item is loaded while tile 1 still works
@@ -92,8 +96,24 @@ struct Item {
 template <bool GEN>
 __device__ __forceinline__ Item decode_item(const FwdArgs& a, int w, int n_pairs) {
   Item it;
-  const int bh = w / n_pairs;
-  const int mp = n_pairs - 1 - (w - bh * n_pairs);  // longest pair of the head first
+  // Heads in order, the longest (latest causal) pair of a head first: the CTAs running at any moment share few
+  // heads' K/V in L2.  Only the last items are ordered differently: over the final kTailWaves waves the pairs of
+  // the remaining heads are taken longest first ACROSS those heads, so that what is drawn last is short and the
+  // CTAs finish together (in head order the last head's longest pair, an eighth of a CTA's whole share of
+  // config 2, would be drawn when most CTAs are nearly done).  Those heads' K/V together fit L2.
+  const int n_heads = a.B * a.Hq;
+  int tail_heads = (kTailWaves * static_cast<int>(gridDim.x) + n_pairs - 1) / n_pairs;
+  if (tail_heads > n_heads) tail_heads = n_heads;
+  const int w0 = (n_heads - tail_heads) * n_pairs;
+  int bh, mp;
+  if (w < w0) {
+    bh = w / n_pairs;
+    mp = n_pairs - 1 - (w - bh * n_pairs);
+  } else {
+    const int x = w - w0, rank = x / tail_heads;
+    bh = n_heads - tail_heads + (x - rank * tail_heads);
+    mp = n_pairs - 1 - rank;
+  }
   it.b = bh / a.Hq;
   it.h = bh - it.b * a.Hq;
   it.hk = it.h / (a.Hq / a.Hkv);
