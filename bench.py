@@ -518,15 +518,23 @@ def run_ours(args, w, wname):
         the whole configuration's work over the slowest rank's time.  Then the optional all-gather of O."""
         from tinytorch_b200 import shard
         n_units = wl["B"] * wl["Hkv"]
-        u0, u1 = shard.unit_range(n_units, rank, world)
         g = wl["Hq"] // wl["Hkv"]
+        decode = wl["kind"] == "decode"
+        ranges = None
+        if decode:
+            # lengths belong to sequences; every unit of a sequence carries its sequence's length.  Units are
+            # split by work (valid cache rows), not by count: equal counts of config 4's units differ by up to
+            # 36 % in rows at 8 ranks, and the slowest rank is the time
+            lens_b = np.random.default_rng(1234).integers(1024, wl["S"] + 1, size=wl["B"]).astype(np.int32)
+            lens_all = np.repeat(lens_b, wl["Hkv"])
+            ranges = shard.balanced_ranges(lens_all.tolist(), world)
+            u0, u1 = ranges[rank]
+        else:
+            u0, u1 = shard.unit_range(n_units, rank, world)
         sw = dict(wl, B=u1 - u0, Hq=g, Hkv=1)  # a unit is one kv head with its g query heads: a batch entry of its own
         q, k, v = build_inputs(sw, 4321)
-        decode = wl["kind"] == "decode"
         if decode:
-            # lengths belong to sequences; every unit of a sequence carries its sequence's length
-            lens_b = np.random.default_rng(1234).integers(1024, wl["S"] + 1, size=wl["B"]).astype(np.int32)
-            lens_u = np.repeat(lens_b, wl["Hkv"])[u0:u1].copy()
+            lens_u = lens_all[u0:u1].copy()
             lens = torch.from_numpy(lens_u).to(dev)
             fn = lambda: op.sdpAttentionDecode(q, k, v, lens)
             total = decode_bytes(wl, lens_b)
@@ -542,13 +550,16 @@ def run_ours(args, w, wname):
         def gather():
             side.wait_stream(torch.cuda.current_stream(dev))
             with torch.cuda.stream(side):
-                out = shard.all_gather_output(o_view, n_units, world, group_size=g)
+                out = shard.all_gather_output(o_view, n_units, world, group_size=g, ranges=ranges)
             torch.cuda.current_stream(dev).wait_stream(side)
             return out
         gsec = timed(gather, 3, 1)
         div = 1e9 if decode else 1e12
         return {"value": total * steps / sec / div, "unit": "GB/s" if decode else "TFLOP/s",
-                "ms_per_step": sec / steps * 1e3, "units_per_rank": [n_units // world, -(-n_units // world)],
+                "ms_per_step": sec / steps * 1e3,
+                "units_per_rank": ([e - b for b, e in ranges] if ranges else [n_units // world, -(-n_units // world)]),
+                "partition": "contiguous unit ranges of equal work (valid cache rows)" if ranges
+                else "contiguous unit ranges of equal size",
                 "allgather_ms": gsec / 3 * 1e3, "allgather_bytes": wl["B"] * wl["Hq"] * wl["L"] * wl["D"] * ESIZE[wl["dtype"]],
                 "scaling": "strong", "config": config_of(wl, name)}
 

@@ -21,6 +21,23 @@ def test_unit_range_covers_everything():
             assert max(sizes) - min(sizes) <= 1
 
 
+def test_balanced_ranges_even_out_ragged_work():
+    rng = np.random.default_rng(3)
+    lens = np.repeat(rng.integers(1024, 8193, size=64), 32)  # config 4: every kv head of a sequence has its length
+    for w in (1, 2, 3, 4, 8):
+        rs = shard.balanced_ranges(lens.tolist(), w)
+        assert rs[0][0] == 0 and rs[-1][1] == len(lens)
+        assert all(rs[i][1] == rs[i + 1][0] for i in range(w - 1))
+        sums = [int(lens[b:e].sum()) for b, e in rs]
+        assert max(sums) <= 1.01 * (sum(sums) / w)
+        eq = [int(lens[slice(*shard.unit_range(len(lens), r, w))].sum()) for r in range(w)]
+        assert max(sums) <= max(eq)
+    # more ranks than units, and zero weights
+    assert shard.balanced_ranges([5.0], 3) in ([(0, 0), (0, 1), (1, 1)], [(0, 1), (1, 1), (1, 1)], [(0, 0), (0, 0), (0, 1)])
+    rs = shard.balanced_ranges([0, 0, 0, 0], 2)
+    assert rs[0][0] == 0 and rs[-1][1] == 4 and rs[0][1] == rs[1][0]
+
+
 def test_shard_is_a_view_and_keeps_groups_together():
     q = torch.arange(2 * 8 * 3 * 4, dtype=torch.float32).view(2, 8, 3, 4)  # Hq = 8
     k = torch.arange(2 * 2 * 3 * 4, dtype=torch.float32).view(2, 2, 3, 4)  # Hkv = 2 -> 4 kv units
@@ -77,6 +94,12 @@ def _worker_empty(rank, world, port, out_dir):
     for gs in (g, None):  # group size given / agreed on by the ranks
         got = shard.all_gather_output(local, 1, world, group_size=gs)
         ok = ok and torch.equal(got, full[0])
+    # explicit (work-balanced) ranges: three units of g heads, split 2 + 1
+    full3 = torch.arange(3 * g * L * D, dtype=torch.float32).view(1, 3 * g, L, D)
+    rs = [(0, 2), (2, 3)]
+    b0, b1 = rs[rank]
+    got = shard.all_gather_output(full3[:, b0 * g:b1 * g], 3, world, group_size=g, ranges=rs)
+    ok = ok and torch.equal(got, full3[0])
     open(os.path.join(out_dir, "rank%d.%s" % (rank, "ok" if ok else "bad")), "w").close()
     dist.destroy_process_group()
 

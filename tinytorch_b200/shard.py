@@ -22,6 +22,25 @@ def unit_range(n_units, rank, world):
     return begin, begin + base + (1 if rank < rem else 0)
 
 
+def balanced_ranges(weights, world):
+    """Contiguous [begin, end) per rank with near-equal total weight (e.g. the valid cache rows of each unit
+    in decode, where equal counts of units can differ by a third in work).  Ranges cover all units in order;
+    a rank may get none.  Deterministic in (weights, world), so every rank computes the same list."""
+    if world <= 0:
+        raise ValueError("bad world")
+    n = len(weights)
+    total = float(sum(weights))
+    bounds, acc, u = [0], 0.0, 0
+    for r in range(1, world):
+        target = total * r / world
+        while u < n and acc + weights[u] / 2.0 <= target:  # a unit goes to the side its middle falls on
+            acc += weights[u]
+            u += 1
+        bounds.append(u)
+    bounds.append(n)
+    return [(bounds[r], bounds[r + 1]) for r in range(world)]
+
+
 def shard_bh(t, n_kv_units, rank, world):
     """View of the rank's units of a dense [B, H, S, D] tensor as [1, units*g, S, D].
 
@@ -35,14 +54,17 @@ def shard_bh(t, n_kv_units, rank, world):
     return t.view(B * H, S, D)[b0 * g:b1 * g].unsqueeze(0)
 
 
-def all_gather_output(o_local, n_kv_units, world, group=None, group_size=None):
+def all_gather_output(o_local, n_kv_units, world, group=None, group_size=None, ranges=None):
     """Gather per-rank O shards ([1, units_r*g, L, D]) into [sum units*g, L, D].
 
     Uses all_gather on equal-sized padded blocks when shard sizes differ.  `group_size` is g, the number of
     query heads per kv head; when it is not given it is taken from the largest local shard over the ranks
-    (a rank without units cannot tell from its own, empty shard).
+    (a rank without units cannot tell from its own, empty shard).  `ranges`: the per-rank unit ranges when
+    they are not the equal-count ones of unit_range (see balanced_ranges).
     """
-    sizes = [unit_range(n_kv_units, r, world) for r in range(world)]
+    sizes = list(ranges) if ranges is not None else [unit_range(n_kv_units, r, world) for r in range(world)]
+    if len(sizes) != world or sizes[0][0] != 0 or sizes[-1][1] != n_kv_units:
+        raise ValueError("ranges must cover the units in rank order")
     mine = sizes[dist.get_rank(group)]
     if group_size is None:
         units = mine[1] - mine[0]
