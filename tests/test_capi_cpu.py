@@ -96,7 +96,7 @@ def test_workspace_sizes(lib):
     assert w(_capi.KIND_FWD, 0, 2, 4, 4, 128, 128, 64) == 0
     assert w(_capi.KIND_BWD, 0, 8, 16, 16, 2048, 2048, 64) == 8 * 16 * 2048 * 4
     # fp16 / bf16: plus the fp32 dQ accumulator
-    assert w(_capi.KIND_BWD, 1, 8, 16, 16, 2048, 2048, 64) == 8 * 16 * 2048 * 4 * (1 + 64)
+    assert w(_capi.KIND_BWD, 1, 8, 16, 16, 2048, 2048, 64) == 8 * 16 * 2048 * 4 * (1 + 64) + 256
     # decode: 512-row chunks -> 16 splits at capacity 8192; (D + 2) floats per (b, h, split)
     assert w(_capi.KIND_DECODE, 2, 64, 32, 32, 1, 8192, 128) == 64 * 32 * 16 * 130 * 4
     assert w(_capi.KIND_DECODE, 2, 64, 32, 32, 1, 512, 128) == 0

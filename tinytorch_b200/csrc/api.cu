@@ -127,7 +127,8 @@ size_t tt_attn_workspace_bytes(int kind, int dtype, int B, int Hq, int Hkv, int 
   if (kind == TT_ATTN_KIND_BWD) {
     // delta [B,Hq,Lq] fp32; the fp16 / bf16 path adds an fp32 dQ accumulator [B,Hq,Lq,D]
     const size_t rows = static_cast<size_t>(B) * Hq * (Lq > 0 ? Lq : 0);
-    return round256(rows * sizeof(float)) + (dtype == TT_ATTN_F32 ? 0 : round256(rows * D * sizeof(float)));
+    // and the persistent kernel's work counter
+    return round256(rows * sizeof(float)) + (dtype == TT_ATTN_F32 ? 0 : round256(rows * D * sizeof(float)) + 256);
   }
   if (kind == TT_ATTN_KIND_DECODE_APPEND) {
     // the decode scratch; on the grouped-query tensor-core path also the rotated q and the new lengths
@@ -228,6 +229,7 @@ int tt_attn_bwd(const tt_attn_bwd_params* p) {
   a.delta = static_cast<float*>(ws.ptr);
   a.dq_accum = reinterpret_cast<float*>(static_cast<char*>(ws.ptr) +
                                         round256(static_cast<size_t>(p->B) * p->Hq * p->Lq * sizeof(float)));
+  a.sched = p->dtype == TT_ATTN_F32 ? nullptr : reinterpret_cast<int*>(static_cast<char*>(ws.ptr) + need - 256);
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   cudaError_t e = p->dtype == TT_ATTN_F32 ? launch_bwd_simt(p->dtype, p->D, a, stream)
                                           : launch_bwd_tc(p->dtype, p->D, a, p->device, stream);

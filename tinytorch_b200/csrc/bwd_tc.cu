@@ -8,8 +8,10 @@
 //   dS = P o (dP - delta) * scale          delta = rowsum(dO o O)
 //   dV = P^T dO      dK = dS^T Q      dQ = dS K
 //
-// One CTA owns a 128-row key tile of one (batch, kv head) and walks the query
-// tiles that see it (and the query heads of its group).  Everything is kept
+// A work item is a 128-row key tile of one (batch, kv head): the CTA walks the query
+// tiles that see it (and the query heads of its group).  CTAs are persistent, one per
+// SM, and draw items from a counter; the first products of the next item are issued
+// while the last dQ of this one is computed and dV / dK are read out.  Everything is kept
 // TRANSPOSED so that a TMEM lane is a key row:
 //   S^T  = K Q^T   (SS MMA, both operands K-major)         -> TMEM region A
 //   dP^T = V dO^T  (SS MMA)                                -> TMEM region B
@@ -22,7 +24,7 @@
 //   dQ   = dS K      (A = dS^T tile in shared memory read MN-major, i.e. as dS;
 //                     B = K tile read MN-major)             -> its own TMEM columns
 //                     when D = 64, else region A
-// dV and dK accumulate in TMEM over the whole walk and are written once.  dQ of a
+// dV and dK accumulate in TMEM over the whole walk of an item and are written once.  dQ of a
 // (key tile, query tile) pair is added to an fp32 buffer through swizzled staging
 // tiles and TMA reductions (cp.reduce.async.bulk.tensor ... add) and converted to
 // the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
@@ -39,14 +41,15 @@ namespace {
 
 constexpr int BM = 128;  // key rows per CTA (= TMEM lanes)
 constexpr int BQ = 128;  // query rows per step
-constexpr int kThreads = 576;  // four compute warpgroups (32 queries of every step each) + producer warp + issuer warp
-constexpr int kCompute = 512;
-constexpr int kReaders = 256;  // D = 64: warpgroups 0 and 1 move dQ out of TMEM (D = 128: all four do)
+constexpr int kCompute = 512;  // four compute warpgroups
 constexpr int kTmemCols = 512;
 constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-row tile
 
 struct __align__(8) SmemCtl {
-  uint64_t kv_full;
+  uint64_t kv_full[2], kv_empty[2];    // K / V stages (work items alternate between them where two fit)
+  uint64_t acc_free;                   // dV / dK of the previous item have been read out of TMEM
+  uint64_t item_full[2], item_empty[2];
+  int item[2];
   uint64_t q_full[2], q_empty[2];
   uint64_t sp_full, pds_half, pds_full, acc_full;  // pds_half: the first 16 queries of every warpgroup are done
   uint64_t dq_full[2], dq_free[2];  // per dQ buffer
@@ -64,12 +67,21 @@ struct Cfg {
   // after the other.
   static constexpr bool kPipe = (D == 64);
   static constexpr int NQ = kPipe ? 2 : 1;         // Q / dO ring depth
+  static constexpr int NKV = kPipe ? 2 : 1;        // K / V stages: the next work item's tiles load under this one's steps
+  // Warps: 16 compute (four warpgroups, 32 queries of every step each); D = 64: a warpgroup that drains results
+  // from TMEM; then the producer warp and the issuer warp (D = 64: in a warpgroup of their own, filled up with
+  // two idle warps, because register reallocation works on whole warpgroups).
+  static constexpr int kProdWarp = kPipe ? 20 : 16, kIssWarp = kProdWarp + 1;
+  static constexpr int kThreads = kPipe ? 768 : 576;
+  static constexpr int kItemConsumers = 1 + kCompute + (kPipe ? BM : 0);  // issuing lane, compute threads, drain
+  static constexpr int kDqReaders = kPipe ? BM : kCompute;  // threads that move a step's dQ out of TMEM
+  static constexpr int kAccReaders = kPipe ? BM : 2 * BM;   // threads that move dV / dK out
   static constexpr int NDS = kPipe ? 2 : 1;        // dS^T tiles
   static constexpr int kDsBytes = BM * BQ * 2;     // one dS^T tile
-  // dQ staging: boxes of 128 rows x 32 floats, one per warpgroup that drains (two with D = 64, four with D = 128)
-  static constexpr int kDqStage = (kPipe ? 2 : 4) * BQ * 128;
-  static constexpr int kVecBytes = 2 * 2 * BQ * 4; // lse / delta vectors, double buffered
-  static constexpr int kSmem = 2 * TB + 2 * NQ * TB + NDS * kDsBytes + kDqStage + kVecBytes + 256;
+  // dQ staging: boxes of 128 rows x 32 floats, D / 32 of them
+  static constexpr int kDqStage = (D / 32) * BQ * 128;
+  static constexpr int kVecBytes = 2 * 2 * BQ * 4; // lse / delta vectors per Q / dO stage
+  static constexpr int kSmem = 2 * NKV * TB + 2 * NQ * TB + NDS * kDsBytes + kDqStage + kVecBytes + 256;
   static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
 };
 
@@ -87,13 +99,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // GEN: the general variant (a mask and / or a causal triangle that is not top-left
 // aligned); the fast variant compiles all of that out.
 template <int D, bool BF16, bool GEN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
     bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmdQ, const BwdArgs a) {
   using C = Cfg<D>;
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-  constexpr int TB = C::TB, NQ = C::NQ, HALVES = D / 64;
+  constexpr int TB = C::TB, NQ = C::NQ, NKV = C::NKV, HALVES = D / 64;
   constexpr bool kPipe = C::kPipe;
   // 128-byte-swizzled tiles must start on a 1024-byte boundary; with D = 128 there is
   // no room for alignment slack, so the array itself carries the requirement
@@ -102,27 +114,33 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (threadIdx.x == 0 && a.status) atomicOr(a.status, kStatusBadSmemAlign);
     return;
   }
-  uint8_t* sK = smem;
-  uint8_t* sV = sK + TB;
-  uint8_t* sQ = sV + TB;          // NQ tiles
-  uint8_t* sdO = sQ + NQ * TB;    // NQ tiles
+  uint8_t* sKV = smem;               // NKV stages of [K tile | V tile]
+  uint8_t* sQ = sKV + NKV * 2 * TB;  // NQ tiles
+  uint8_t* sdO = sQ + NQ * TB;       // NQ tiles
   uint8_t* sdS = sdO + NQ * TB;   // NDS x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
-  uint8_t* sdq = sdS + C::NDS * C::kDsBytes;  // dQ staging: per draining warpgroup [128 queries][32 floats], swizzled
-  float* svec = reinterpret_cast<float*>(sdq + C::kDqStage);  // [2 buffers][lse2 | delta][128]
+  uint8_t* sdq = sdS + C::NDS * C::kDsBytes;  // dQ staging: boxes of [128 queries][32 floats], swizzled
+  float* svec = reinterpret_cast<float*>(sdq + C::kDqStage);  // [NQ stages][lse2 | delta][128]
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(reinterpret_cast<uint8_t*>(svec) + C::kVecBytes);
   volatile int* abort_flag = &ctl->abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // key tiles near the start see the most query tiles under the causal mask: launch them first
-  // CTAs start in the order of the linear block index.  Heads in order, and within a head the key tiles in
-  // order: under the causal mask the first key tile is seen by every query tile and walks longest.  Only the
-  // last `tail_heads` heads are ordered differently, key tile by key tile ACROSS those heads, so that the CTAs
-  // started last are the short ones and the grid ends together (in head order the last head's first key tile,
-  // the longest walk there is, would start when most SMs are nearly done).
+  // Persistent CTAs draw work items (a key tile of one (batch, kv head)) from a counter, so that the start of
+  // an item (K / V load, first products) and the end of the one before (read-out of dV / dK) overlap instead of
+  // costing every key tile a CTA launch, a ramp and a drain.  Heads in order, and within a head the key tiles
+  // in order: under the causal mask the first key tile is seen by every query tile and walks longest.  Only the
+  // last `tail_heads` heads are ordered differently, key tile by key tile ACROSS those heads, so that the items
+  // drawn last are the short ones and the CTAs finish together.
+  const int group = a.Hq / a.Hkv;
   const int n_kt = (a.Skv + BM - 1) / BM, n_heads = a.Hkv * a.B;
-  int nt, bh;
-  {
-    const int w = blockIdx.x, w0 = (n_heads - a.tail_heads) * n_kt;
+  const int n_items = n_kt * n_heads;
+  const int n_q_tiles = (a.Lq + BQ - 1) / BQ;
+  struct Item {
+    int hk, b, kv0, kv_len, shift, qt_begin, per_head, n_steps;
+  };
+  auto decode_item = [&](int w) {
+    Item it;
+    const int w0 = (n_heads - a.tail_heads) * n_kt;
+    int bh, nt;
     if (w < w0) {
       bh = w / n_kt;
       nt = w - bh * n_kt;
@@ -131,40 +149,40 @@ __global__ void __launch_bounds__(kThreads, 1)
       nt = x / a.tail_heads;
       bh = n_heads - a.tail_heads + (x - nt * a.tail_heads);
     }
-  }
-  const int b = bh / a.Hkv, hk = bh - b * a.Hkv;
-  const int group = a.Hq / a.Hkv;
-  const int kv0 = nt * BM;
-  int kv_len = a.Skv;
-  if (a.kv_lens) {
-    int l = a.kv_lens[b];
-    kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
-  }
-  const int n_q_tiles = (a.Lq + BQ - 1) / BQ;
-  const int shift = GEN ? causal_shift(a.causal, kv_len, a.Lq) : 0;  // key j participates iff j <= i + shift
-  // BM == BQ: query tiles before the key tile see none of it (general: first tile with a row i >= kv0 - shift)
-  const int qt_begin = a.causal ? (GEN ? (kv0 - shift > 0 ? (kv0 - shift) / BQ : 0) : nt) : 0;
-  const int per_head = (kv0 < kv_len && qt_begin < n_q_tiles) ? n_q_tiles - qt_begin : 0;
-  const int n_steps = per_head * group;
+    it.b = bh / a.Hkv, it.hk = bh - it.b * a.Hkv;
+    it.kv0 = nt * BM;
+    int kv_len = a.Skv;
+    if (a.kv_lens) {
+      int l = a.kv_lens[it.b];
+      kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
+    }
+    it.kv_len = kv_len;
+    it.shift = GEN ? causal_shift(a.causal, kv_len, a.Lq) : 0;  // key j participates iff j <= i + shift
+    // BM == BQ: query tiles before the key tile see none of it (general: first tile with a row i >= kv0 - shift)
+    it.qt_begin = a.causal ? (GEN ? (it.kv0 - it.shift > 0 ? (it.kv0 - it.shift) / BQ : 0) : nt) : 0;
+    it.per_head = (it.kv0 < kv_len && it.qt_begin < n_q_tiles) ? n_q_tiles - it.qt_begin : 0;
+    it.n_steps = it.per_head * group;
+    return it;
+  };
 
-  if (warp == 16 && lane == 0) {
-    ptx::mbar_init(&ctl->kv_full, 1);
+  if (warp == C::kProdWarp && lane == 0) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&ctl->kv_full[i], 1);
+      ptx::mbar_init(&ctl->kv_empty[i], 1);
+      ptx::mbar_init(&ctl->item_full[i], 1);
+      ptx::mbar_init(&ctl->item_empty[i], C::kItemConsumers);
       ptx::mbar_init(&ctl->q_full[i], 1);
       ptx::mbar_init(&ctl->q_empty[i], 1);
+      ptx::mbar_init(&ctl->vec_full[i], 32);  // the lanes of the producer warp
+      ptx::mbar_init(&ctl->dq_full[i], 1);
+      ptx::mbar_init(&ctl->dq_free[i], C::kDqReaders);
     }
+    ptx::mbar_init(&ctl->acc_free, C::kAccReaders);
     ptx::mbar_init(&ctl->sp_full, 1);
     ptx::mbar_init(&ctl->pds_full, kCompute);
     ptx::mbar_init(&ctl->pds_half, kCompute);
     ptx::mbar_init(&ctl->acc_full, 1);
-    ptx::mbar_init(&ctl->vec_full[0], BM);
-    ptx::mbar_init(&ctl->vec_full[1], BM);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&ctl->dq_full[i], 1);
-      ptx::mbar_init(&ctl->dq_free[i], kPipe ? kReaders : kCompute);
-    }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);
@@ -173,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tma_prefetch_desc(&tmdO);
     ptx::tma_prefetch_desc(&tmdQ);
   }
-  if (warp == 17) {
+  if (warp == C::kIssWarp) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -185,38 +203,159 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
   const uint32_t tdV = tmem + 256;       // D columns
   const uint32_t tdK = tmem + 256 + D;   // D columns
-  // dQ of step n: two buffers of D columns when there is room (D = 64), so that the
+  // dQ of running step g: two buffers of D columns when there is room (D = 64), so that the
   // read-out of one step overlaps the MMAs of the next; else region A is reused
-  auto tdQ = [&](int n) { return kPipe ? tmem + 384 + (n & 1) * D : tA; };
+  auto tdQ = [&](uint32_t g) { return kPipe ? tmem + 384 + (g & 1) * D : tA; };
 
-  if (warp == 16) {
-    // -------------------------------------------------------------- producer --
-    if (lane == 0 && n_steps > 0) {
-      ptx::mbar_arrive_expect_tx(&ctl->kv_full, 2 * TB);
+  // Every role below walks the same sequence of items and, within an item, of steps; g counts the steps over
+  // all items of this CTA (per-step barriers and buffers go by it), k the items (per-item barriers).
+  //
+  // dQ of step n of an item -> global: thread r owns query row q0 + r; 32-float column boxes go through
+  // swizzled staging tiles and TMA reductions (coalesced; rows beyond Lq are clipped by the tensor map).
+  // dV / dK: thread r owns key row kv0 + r and writes its D elements directly.
+  auto store_acc_row = [&](T* out, const uint32_t (&v)[32]) {
 #pragma unroll
-      for (int hf = 0; hf < HALVES; ++hf) {
-        ptx::tma_load_4d(sK + hf * kHalfBytes, &tmK, &ctl->kv_full, hf * 64, kv0, hk, b);
-        ptx::tma_load_4d(sV + hf * kHalfBytes, &tmV, &ctl->kv_full, hf * 64, kv0, hk, b);
-      }
-      for (int n = 0; n < n_steps; ++n) {
-        const int st = n % NQ;
-        const uint32_t ph = (n / NQ) & 1;
-        const int h = hk * group + n / per_head;
-        const int q0 = (qt_begin + n % per_head) * BQ;
-        if (!ptx::mbar_wait(&ctl->q_empty[st], ph ^ 1, abort_flag)) break;
-        ptx::mbar_arrive_expect_tx(&ctl->q_full[st], 2 * TB);
-#pragma unroll
-        for (int hf = 0; hf < HALVES; ++hf) {
-          ptx::tma_load_4d(sQ + st * TB + hf * kHalfBytes, &tmQ, &ctl->q_full[st], hf * 64, q0, h, b);
-          ptx::tma_load_4d(sdO + st * TB + hf * kHalfBytes, &tmdO, &ctl->q_full[st], hf * 64, q0, h, b);
-        }
-      }
+    for (int i = 0; i < 32; i += 8) {
+      uint4 w4;
+      w4.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+      w4.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      w4.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+      w4.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+      *reinterpret_cast<uint4*>(out + i) = w4;
     }
-  } else if (warp == 17) {
-    // ---------------------------------------------------------------- issuer --
-    // The whole warp runs the loop (waits made uniform by a vote); one elected lane issues, so that addresses
-    // and descriptors stay warp-uniform.
-    if (n_steps > 0) {
+  };
+
+  if ((warp >> 2) == (C::kProdWarp >> 2)) {
+    // (D = 64: 96 registers for the 512 compute threads, 48 for the other 256: together the 80 x 768 the CTA
+    // was launched with, so the increase can always be served)
+    if constexpr (kPipe) ptx::setmaxnreg_dec<48>();
+    if (warp == C::kProdWarp) {
+      // ------------------------------------------------------------ producer --
+      // Lane 0 draws the items, publishes those with steps to the other warps and feeds their tiles by TMA; the
+      // whole warp fetches the per-query vectors of every step (-lse * log2(e) and -delta * scale) into the
+      // step's stage.  A key tile that no query sees has no steps: the warp writes its zero gradients here and
+      // nobody else hears of it (so a run of such items cannot fill the two-slot queue while the issuer looks
+      // one item ahead).
+      uint32_t gq = 0;  // steps requested in earlier items (ring position)
+      bool dep_waited = false;
+      // per-query vectors of running step g into buffer g & 1
+      auto fetch_vec = [&](const Item& it, int n, uint32_t g) {
+        if (!dep_waited) {
+          // This kernel is launched early behind the delta pre-pass: barriers, TMEM and the first loads need
+          // only the inputs; delta is first read here.
+          ptx::grid_dep_wait();
+          dep_waited = true;
+        }
+        const int h = it.hk * group + n / it.per_head;
+        const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+        float lv[4], dl[4];
+        const int64_t base = (static_cast<int64_t>(it.b) * a.Hq + h) * a.Lq + q0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = j * 32 + lane;
+          lv[j] = -INFINITY;  // rows beyond Lq behave like rows without any participating key: P = 0
+          dl[j] = 0.f;
+          if (q0 + row < a.Lq) {
+            lv[j] = a.lse[base + row];
+            dl[j] = a.delta[base + row];
+          }
+        }
+        float* nv = svec + (g & 1) * 2 * BQ;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = j * 32 + lane;
+          nv[row] = lv[j] == -INFINITY ? -INFINITY : -lv[j] * kLog2e;
+          nv[BQ + row] = -dl[j] * a.scale;
+        }
+        ptx::mbar_arrive(&ctl->vec_full[g & 1]);
+      };
+      for (uint32_t i = 0;;) {  // i: items published so far
+        int w = 0;
+        if (lane == 0) {
+          w = atomicAdd(a.sched, 1);
+          if (w >= n_items) w = -1;
+        }
+        w = __shfl_sync(0xffffffffu, w, 0);
+        Item it = {};
+        if (w >= 0) {
+          it = decode_item(w);
+          if (it.n_steps == 0) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              void* base = t == 0 ? a.dv : a.dk;
+              const Str3& st = t == 0 ? a.dvs : a.dks;
+              if (!base) continue;
+              T* out = reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h;
+              for (int e = lane; e < BM * (D / 8); e += 32) {
+                const int row = it.kv0 + e / (D / 8);
+                if (row < a.Skv)
+                  *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * st.s + (e % (D / 8)) * 8) =
+                      make_uint4(0, 0, 0, 0);
+              }
+            }
+            continue;
+          }
+        }
+        int ok = 1;
+        if (lane == 0) {
+          const int slot = i & 1;
+          ok = ptx::mbar_wait(&ctl->item_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
+          if (ok) {
+            ctl->item[slot] = w;
+            ptx::mbar_arrive(&ctl->item_full[slot]);
+          }
+          if (ok && w >= 0) {
+            // every MMA that read this stage (NKV items ago) has completed
+            const int ks = i % NKV;
+            uint8_t* sK = sKV + ks * 2 * TB;
+            uint8_t* sV = sK + TB;
+            ok = ptx::mbar_wait(&ctl->kv_empty[ks], ((i / NKV) & 1) ^ 1, abort_flag);
+            if (ok) {
+              ptx::mbar_arrive_expect_tx(&ctl->kv_full[ks], 2 * TB);
+#pragma unroll
+              for (int hf = 0; hf < HALVES; ++hf) {
+                ptx::tma_load_4d(sK + hf * kHalfBytes, &tmK, &ctl->kv_full[ks], hf * 64, it.kv0, it.hk, it.b);
+                ptx::tma_load_4d(sV + hf * kHalfBytes, &tmV, &ctl->kv_full[ks], hf * 64, it.kv0, it.hk, it.b);
+              }
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok || w < 0) break;
+        for (int n = 0; n < it.n_steps; ++n) {
+          const uint32_t g = gq + n;
+          const int st = g % NQ;
+          const int h = it.hk * group + n / it.per_head;
+          const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+          // With a single Q / dO stage the vectors (two buffers) are fetched a step ahead of the tiles: the wait
+          // passed for the tiles of step g - 1 says that step g - 2, the last to read this buffer, is over.
+          const bool vec_first = NQ == 1 && g > 0;
+          if (vec_first) fetch_vec(it, n, g);
+          if (lane == 0) {
+            // the MMAs that read the stage's Q / dO have completed, and with them the element-wise phase that
+            // read its vectors
+            ok = ptx::mbar_wait(&ctl->q_empty[st], ((g / NQ) & 1) ^ 1, abort_flag);
+            if (ok) {
+              ptx::mbar_arrive_expect_tx(&ctl->q_full[st], 2 * TB);
+#pragma unroll
+              for (int hf = 0; hf < HALVES; ++hf) {
+                ptx::tma_load_4d(sQ + st * TB + hf * kHalfBytes, &tmQ, &ctl->q_full[st], hf * 64, q0, h, it.b);
+                ptx::tma_load_4d(sdO + st * TB + hf * kHalfBytes, &tmdO, &ctl->q_full[st], hf * 64, q0, h, it.b);
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          if (!vec_first) fetch_vec(it, n, g);
+        }
+        if (!ok) break;
+        gq += it.n_steps;
+        ++i;
+      }
+    } else if (warp == C::kIssWarp) {
+      // -------------------------------------------------------------- issuer --
+      // The whole warp runs the loop (waits made uniform by a vote); one elected lane issues, so that addresses
+      // and descriptors stay warp-uniform.
       const bool leader = ptx::elect_one();
       auto uwait = [&](uint64_t* bar, uint32_t parity) {
         return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
@@ -226,304 +365,977 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ, fmt, 0, 0);   // S^T, dP^T: N = queries
       const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);  // dV, dK: A from TMEM, B MN-major
       const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);   // dQ: both operands MN-major
-      const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
-      const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
-      const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK), kHalfBytes);
-      bool ok = uwait(&ctl->kv_full, 0);
-      auto stage_lo = [&](const uint8_t* base, int n, uint32_t lbo) {
-        return ptx::smem_desc_lo(ptx::smem_u32(base + (n % NQ) * TB), lbo);
+      auto klo = [&](uint32_t k) { return ptx::smem_desc_lo(ptx::smem_u32(sKV + (k % NKV) * 2 * TB), 16); };
+      auto vlo = [&](uint32_t k) { return ptx::smem_desc_lo(ptx::smem_u32(sKV + (k % NKV) * 2 * TB + TB), 16); };
+      auto klo_mn = [&](uint32_t k) {
+        return ptx::smem_desc_lo(ptx::smem_u32(sKV + (k % NKV) * 2 * TB), kHalfBytes);
       };
-      // S^T = K Q^T and dP^T = V dO^T of step n
-      auto issue_s_dp = [&](int n) {
-        if (!uwait(&ctl->q_full[n % NQ], (n / NQ) & 1)) return false;
+      auto stage_lo = [&](const uint8_t* base, uint32_t g, uint32_t lbo) {
+        return ptx::smem_desc_lo(ptx::smem_u32(base + (g % NQ) * TB), lbo);
+      };
+      uint32_t fi = 0;  // items taken from the queue
+      // the next item, or false: none is left or a wait ran out
+      auto fetch = [&](Item& it) {
+        const int slot = fi & 1;
+        if (!uwait(&ctl->item_full[slot], (fi >> 1) & 1)) return false;
+        const int w = ctl->item[slot];
+        __syncwarp();  // every lane has read the slot
+        if (leader) ptx::mbar_arrive(&ctl->item_empty[slot]);
+        ++fi;
+        if (w < 0) return false;
+        it = decode_item(w);
+        return true;
+      };
+      // K / V of the k-th item of this CTA are in shared memory
+      auto kv_ready = [&](uint32_t k) { return uwait(&ctl->kv_full[k % NKV], (k / NKV) & 1); };
+      // S^T = K Q^T and dP^T = V dO^T of running step g, on the tiles of the CTA's k-th item
+      auto issue_s_dp = [&](uint32_t g, uint32_t k) {
+        if (!uwait(&ctl->q_full[g % NQ], (g / NQ) & 1)) return false;
         ptx::tc_fence_after();
-        const uint32_t qlo = stage_lo(sQ, n, 16), dolo = stage_lo(sdO, n, 16);
+        const uint32_t qlo = stage_lo(sQ, g, 16), dolo = stage_lo(sdO, g, 16), kl = klo(k), vl = vlo(k);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          if (leader) ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_ss2(tA, kl + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          if (leader) ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_ss2(tB, vl + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
         }
         if (leader) ptx::mma_commit(&ctl->sp_full);
         return true;
       };
-      if (ok) ok = issue_s_dp(0);
-      for (int n = 0; n < n_steps && ok; ++n) {
-        const int st = n % NQ;
-        const uint32_t qlo_mn = stage_lo(sQ, n, kHalfBytes), dolo_mn = stage_lo(sdO, n, kHalfBytes);
-        const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (n % C::NDS) * C::kDsBytes), kHalfBytes);
-        // dV and dK contract over the 128 queries, 16 per k-step (2048 bytes of B).  Warpgroup w forms
-        // the queries of k-step 2w first and of k-step 2w+1 second, so the even k-steps run while the
-        // odd ones are still being computed.
+      Item cur = {}, nxt = {};
+      uint32_t g = 0, k = 0;
+      bool have = fetch(cur);
+      bool ok = have && kv_ready(0) && issue_s_dp(0, 0);
+      while (have && ok) {
+        bool have_next = false;
+        for (int n = 0; n < cur.n_steps && ok; ++n, ++g) {
+          const bool last = n + 1 == cur.n_steps;
+          const int st = g % NQ;
+          const uint32_t qlo_mn = stage_lo(sQ, g, kHalfBytes), dolo_mn = stage_lo(sdO, g, kHalfBytes);
+          const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (g % C::NDS) * C::kDsBytes), kHalfBytes);
+          // dV and dK contract over the 128 queries, 16 per k-step (2048 bytes of B).  Warpgroup w forms
+          // the queries of k-step 2w first and of k-step 2w+1 second, so the even k-steps run while the
+          // odd ones are still being computed.
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if (!(ok = uwait(half == 0 ? &ctl->pds_half : &ctl->pds_full, n & 1))) break;
-          ptx::tc_fence_after();
+          for (int half = 0; half < 2; ++half) {
+            if (!(ok = uwait(half == 0 ? &ctl->pds_half : &ctl->pds_full, g & 1))) break;
+            // the first products of an item overwrite the accumulators: the item before has been read out
+            if (half == 0 && n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
+            ptx::tc_fence_after();
 #pragma unroll
-          for (int ks = half; ks < BQ / 16; ks += 2)
-            if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
-                         (n > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = half; ks < BQ / 16; ks += 2)
+              if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+                           (n > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-          for (int ks = half; ks < BQ / 16; ks += 2)
-            if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
-                         (n > 0 || ks > 0) ? 1u : 0u);
-        }
-        if (!ok) break;
-        if (!kPipe) if (leader) ptx::mma_commit(&ctl->q_empty[st]);  // Q and dO of this step have been read (dV, dK above)
-        if (kPipe) {
-          // P^T / dS^T of this step have been consumed from TMEM (in issue order):
-          // the next step's S^T / dP^T go first, then this step's dQ, which reads
-          // dS^T from shared memory
-          if (n + 1 < n_steps && !(ok = issue_s_dp(n + 1))) break;
-          if (n >= 2 && !(ok = uwait(&ctl->dq_free[n & 1], ((n >> 1) - 1) & 1))) break;
-        }
-#pragma unroll
-        for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
-          if (leader) ptx::mma_ss2(tdQ(n), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
-        }
-        if (leader) ptx::mma_commit(&ctl->dq_full[kPipe ? (n & 1) : 0]);
-        if (kPipe) if (leader) ptx::mma_commit(&ctl->q_empty[st]);
-        if (!kPipe && n + 1 < n_steps) {
-          // (the single Q / dO stage was handed back after dK above, so its reload runs under
-          // the dQ MMAs and the read-out.)  dP^T of the next step can go into region B at once:
-          // dS^T there has been consumed in issue order.  Region A holds this step's dQ until the
-          // compute threads have read it: S^T of the next step waits for that.
-          if (!(ok = uwait(&ctl->q_full[(n + 1) % NQ], ((n + 1) / NQ) & 1))) break;
-          ptx::tc_fence_after();
-          const uint32_t qlo = stage_lo(sQ, n + 1, 16), dolo = stage_lo(sdO, n + 1, 16);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-            if (leader) ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+            for (int ks = half; ks < BQ / 16; ks += 2)
+              if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+                           (n > 0 || ks > 0) ? 1u : 0u);
           }
-          if (!(ok = uwait(&ctl->dq_free[0], n & 1))) break;
-          ptx::tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-            if (leader) ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+          if (!ok) break;
+          // Q and dO of this step have been read, and with these products the step's vectors; after the item's
+          // last step dV and dK are complete
+          if (leader) ptx::mma_commit(&ctl->q_empty[st]);
+          if (last && leader) ptx::mma_commit(&ctl->acc_full);
+          if (kPipe) {
+            // P^T / dS^T of this step have been consumed from TMEM (in issue order):
+            // the next step's S^T / dP^T go first (of the next item after this item's last step: its K / V
+            // sit in the other stage), then this step's dQ, which reads dS^T from shared memory
+            if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
+            if (!ok) break;
+            if ((!last || have_next) && !(ok = issue_s_dp(g + 1, last ? k + 1 : k))) break;
+            if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
           }
-          if (leader) ptx::mma_commit(&ctl->sp_full);
+          const uint32_t kmn = klo_mn(k);
+#pragma unroll
+          for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
+            if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, kmn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+          }
+          if (leader) ptx::mma_commit(&ctl->dq_full[kPipe ? (g & 1) : 0]);
+          // every MMA of the item has been issued: its K / V stage goes back
+          if (last && leader) ptx::mma_commit(&ctl->kv_empty[k % NKV]);
+          if (!kPipe) {
+            if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
+            if (!ok || (last && !have_next)) break;
+            const uint32_t kn = last ? k + 1 : k;
+            // (the single Q / dO stage was handed back after dK above, so its reload runs under
+            // the dQ MMAs and the read-out.)  dP^T of the next step can go into region B at once:
+            // dS^T there has been consumed in issue order.  Region A holds this step's dQ until the
+            // compute threads have read it: S^T of the next step waits for that.
+            if (!(ok = uwait(&ctl->q_full[(g + 1) % NQ], ((g + 1) / NQ) & 1))) break;
+            ptx::tc_fence_after();
+            const uint32_t qlo = stage_lo(sQ, g + 1, 16), dolo = stage_lo(sdO, g + 1, 16), kl = klo(kn), vl = vlo(kn);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+              if (leader) ptx::mma_ss2(tB, vl + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+            }
+            if (!(ok = uwait(&ctl->dq_free[0], g & 1))) break;
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+              if (leader) ptx::mma_ss2(tA, kl + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+            }
+            if (leader) ptx::mma_commit(&ctl->sp_full);
+          }
+        }
+        cur = nxt;
+        have = have_next;
+        ++k;
+      }
+    }
+  } else if (kPipe && (warp >> 2) == 4) {
+    // ----------------------------------------------------------------- drain --
+    // D = 64: a warpgroup of its own moves the results out of TMEM, so that the compute warpgroups go from
+    // one step's element-wise phase straight into the next: dQ of every step (thread r = query row r, both
+    // 32-column boxes), and dV / dK of the item (thread r = key row r) between the last two dQ.
+    ptx::setmaxnreg_dec<48>();
+    if constexpr (kPipe) {
+      const int r = tid & (BM - 1);
+      const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      bool ok = true;
+      ptx::grid_dep_wait();  // the reductions below need the dQ accumulator cleared by the pre-pass
+      uint32_t g = 0;
+      for (uint32_t k = 0;; ++k) {
+        const int slot = k & 1;
+        if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
+        const int w = ok ? ctl->item[slot] : -1;
+        ptx::mbar_arrive(&ctl->item_empty[slot]);
+        // the warpgroup leaves as one (its named barriers count all 128 threads) when any of its waits ran out
+        if (ptx::named_barrier_or(1, BM, !ok)) break;
+        if (w < 0) break;
+        const Item it = decode_item(w);
+        for (int n = 0; n < it.n_steps; ++n, ++g) {
+          if (n + 1 == it.n_steps) {
+            // dV, then dK: complete once the last step's products are (before its dQ)
+            if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
+            ptx::tc_fence_after();
+            const int kv_row = it.kv0 + r;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              void* base = t == 0 ? a.dv : a.dk;
+              const Str3& st = t == 0 ? a.dvs : a.dks;
+              T* out = base ? reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h + static_cast<int64_t>(kv_row) * st.s
+                            : nullptr;
+#pragma unroll
+              for (int cc = 0; cc < D / 32; ++cc) {
+                uint32_t v[32];
+                ptx::tmem_ld32((t == 0 ? tdV : tdK) + lane_addr + cc * 32, v);
+                ptx::tmem_wait_ld();
+                if (t == 1 && cc == D / 32 - 1) {
+                  // the accumulators may be overwritten by the next item's first products
+                  ptx::tc_fence_before();
+                  ptx::mbar_arrive(&ctl->acc_free);
+                }
+                if (ok && out && kv_row < a.Skv) store_acc_row(out + cc * 32, v);
+              }
+            }
+          }
+          const int h = it.hk * group + n / it.per_head;
+          const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+          if (ok) ok = ptx::mbar_wait(&ctl->dq_full[g & 1], (g >> 1) & 1, abort_flag);
+          ptx::tc_fence_after();
+          if (r == 0) ptx::bulk_wait_read();  // the previous reductions have read the staging tiles
+          ptx::named_barrier(1, BM);
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t v[32];
+            ptx::tmem_ld32(tdQ(g) + lane_addr + cc * 32, v);
+            ptx::tmem_wait_ld();
+            if (cc == D / 32 - 1) {
+              ptx::tc_fence_before();
+              ptx::mbar_arrive(&ctl->dq_free[g & 1]);
+            }
+            uint8_t* stage = sdq + cc * (BQ * 128);
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
+                  make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+          }
+          ptx::fence_proxy_async_smem();
+          ptx::named_barrier(1, BM);
+          if (r == 0 && ok) {
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc)
+              ptx::tma_reduce_add_4d(&tmdQ, sdq + cc * (BQ * 128), cc * 32, q0, h, it.b);
+            ptx::bulk_commit();
+          }
         }
       }
-      if (ok) if (leader) ptx::mma_commit(&ctl->acc_full);
+      if (r == 0) ptx::bulk_wait_all();
     }
   } else {
     // --------------------------------------------------------------- compute --
+    if constexpr (kPipe) ptx::setmaxnreg_inc<96>();
     const int wg = warp >> 2;   // which 32 queries of every step
     const int r = tid & (BM - 1);  // key row within the tile (phase 1) / query row of the step (dQ read-out)
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int kv_row = kv0 + r;
-    const bool row_valid = kv_row < kv_len;
     const float c = a.scale * kLog2e;
     const float2 c2v = make_float2(c, c), sc2 = make_float2(a.scale, a.scale);
     bool ok = true;
-    // This kernel is launched early behind the delta pre-pass: loads, barriers, TMEM and the first S^T / dP^T
-    // MMAs need only the inputs; delta and the cleared dQ accumulator are first touched by these threads.
+    // (launched early behind the delta pre-pass: the dQ accumulator it clears is first touched after this wait)
     ptx::grid_dep_wait();
     ptx::grid_dep_launch();  // (the conversion kernel may come up; it waits for this grid)
 
-    // per-query vectors of step n live in svec[(n & 1)]: [0,128) -lse * log2(e), [128,256) -delta * scale;
-    // warpgroup 0 fetches them one step ahead.  load_vec only issues the two loads (raw values: nothing
-    // may depend on them before the step's barrier, or the whole CTA would wait for their latency);
-    // store_vec converts and stores them a step's work later.
-    auto load_vec = [&](int n, float& lse, float& delta) {
-      const int h = hk * group + n / per_head;
-      const int q = (qt_begin + n % per_head) * BQ + r;
-      lse = -INFINITY;  // rows beyond Lq behave like rows without any participating key: P = 0
-      delta = 0.f;
-      if (q < a.Lq) {
-        const int64_t idx = (static_cast<int64_t>(b) * a.Hq + h) * a.Lq + q;
-        lse = a.lse[idx];
-        delta = a.delta[idx];
+    uint32_t g0 = 0;  // running step at the start of the item
+    for (uint32_t k = 0;; ++k) {
+      const int slot = k & 1;
+      if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
+      const int w = ok ? ctl->item[slot] : -1;
+      ptx::mbar_arrive(&ctl->item_empty[slot]);
+      if constexpr (!kPipe) {
+        // a warpgroup leaves as one (its named barriers below count all 128 threads) when any of its waits ran out
+        if (ptx::named_barrier_or(3 + wg, BM, !ok)) break;
       }
-    };
-    auto store_vec = [&](int n, float lse, float delta) {
-      float* nv = svec + (n & 1) * 2 * BQ;
-      nv[r] = lse == -INFINITY ? -INFINITY : -lse * kLog2e;
-      nv[BQ + r] = -delta * a.scale;
-    };
-    if (n_steps > 0 && wg == 0) {
-      float l0, d0;
-      load_vec(0, l0, d0);
-      store_vec(0, l0, d0);
-      ptx::mbar_arrive(&ctl->vec_full[0]);
-    }
-    // dQ of step n -> global; thread r owns query row q0 + r, warpgroup w the columns
-    // [32w, 32w+32) (D = 64: warpgroups 0 and 1; D = 128: all four): through a swizzled
-    // staging tile and one TMA reduction per warpgroup (coalesced; rows beyond Lq are
-    // clipped by the tensor map)
-    auto read_out_dq = [&](int n) {
-      const int h = hk * group + n / per_head;
-      const int q0 = (qt_begin + n % per_head) * BQ;
-      const int buf = kPipe ? (n & 1) : 0;
-      if (ok) ok = ptx::mbar_wait(&ctl->dq_full[buf], (kPipe ? (n >> 1) : n) & 1, abort_flag);
-      ptx::tc_fence_after();
-      uint32_t v[32];
-      ptx::tmem_ld32(tdQ(n) + lane_addr + wg * 32, v);
-      ptx::tmem_wait_ld();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(&ctl->dq_free[buf]);
-      uint8_t* stage = sdq + wg * (BQ * 128);
-      if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging tile
-      ptx::named_barrier(3 + wg, BM);
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-        *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
-            make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
-      ptx::fence_proxy_async_smem();
-      ptx::named_barrier(3 + wg, BM);
-      if (r == 0 && ok) {
-        ptx::tma_reduce_add_4d(&tmdQ, stage, wg * 32, q0, h, b);
-        ptx::bulk_commit();
-      }
-    };
+      if (w < 0) break;
+      const Item it = decode_item(w);
+      const int b = it.b, hk = it.hk, kv0 = it.kv0, kv_len = it.kv_len, shift = it.shift, qt_begin = it.qt_begin,
+                per_head = it.per_head, n_steps = it.n_steps;
+      const int kv_row = kv0 + r;
+      const bool row_valid = kv_row < kv_len;
 
-    for (int n = 0; n < n_steps; ++n) {
-      const int q0 = (qt_begin + n % per_head) * BQ;
-      const float* vec = svec + (n & 1) * 2 * BQ;
-      uint8_t* ds_tile = sdS + (n % C::NDS) * C::kDsBytes;
-      float ln = -INFINITY, dn = 0.f;
-      if (wg == 0 && n + 1 < n_steps) load_vec(n + 1, ln, dn);  // prefetch for the next step
-      // all threads reach this point every step, expired waits included
-      // This step's vectors are in shared memory.  (An mbarrier, not a barrier over the four warpgroups: the two
-      // that drain dQ take longer per step, and the others may go on into the next step's exponentials meanwhile.
-      // Warpgroup 0 cannot overwrite a buffer that is still read: it writes buffer n & 1 again after the first
-      // MMAs of step n + 1 have completed, which every warpgroup's results of step n precede.)
-      if (ok) ok = ptx::mbar_wait(&ctl->vec_full[n & 1], (n >> 1) & 1, abort_flag);
-      if (ok) ok = ptx::mbar_wait(&ctl->sp_full, n & 1, abort_flag);
-      ptx::tc_fence_after();
-      const bool diag = a.causal && q0 + shift < kv0 + BM;  // some (query, key) pairs of this step are masked
-      const bool masked = diag || kv0 + BM > kv_len;
-#pragma unroll
-      for (int sc = 0; sc < 2; ++sc) {
-        const int col = wg * 32 + sc * 16;  // 16 queries of the step
-        uint32_t s[16], dp[16];
-        ptx::tmem_ld16(tA + lane_addr + col, s);
-        ptx::tmem_ld16(tB + lane_addr + col, dp);
-        ptx::tmem_wait_ld();
-        uint32_t pk[8], dk[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(vec + col + i);
-          const float4 d4 = *reinterpret_cast<const float4*>(vec + BQ + col + i);
-          // P = 2^(c*s - lse2), dS = P * (scale*dP - scale*delta), in packed fp32 pairs
-          float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v,
-                                make_float2(l4.x, l4.y));
-          float2 x1 = ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v,
-                                make_float2(l4.z, l4.w));
-          if constexpr (GEN) {
-            if (a.mask.ptr && kv_row < a.Skv) {
-              // the mask element of (query, this thread's key): adjacent threads read adjacent keys
-              const int q = q0 + col + i;
-              const int64_t mo = b * a.mask.sb + (hk * group + n / per_head) * a.mask.sh + q * a.mask.sl + kv_row;
-              if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, mo);
-              if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, mo + a.mask.sl);
-              if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, mo + 2 * a.mask.sl);
-              if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, mo + 3 * a.mask.sl);
-            }
-          }
-          // (one exponential in eight on the FMA pipe: the 16 compute warps saturate the MUFU units in this phase;
-          // one in four is as fast within half a percent, three in eight and more are slower again)
-          float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), (i & 4) ? ptx::ex2_fma(x1.y) : ptx::ex2(x1.y));
-          if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
-            const int q = q0 + col + i + shift;
-            if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
-            if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
-            if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
-            if (!row_valid || (diag && q + 3 < kv_row)) p1.y = 0.f;
-          }
-          const float2 g0 = ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2,
-                                      make_float2(d4.x, d4.y));
-          const float2 g1 = ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2,
-                                      make_float2(d4.z, d4.w));
-          const float2 ds0 = ptx::mul2(p0, g0), ds1 = ptx::mul2(p1, g1);
-          pk[(i >> 1) + 0] = pack2<BF16>(p0.x, p0.y);
-          pk[(i >> 1) + 1] = pack2<BF16>(p1.x, p1.y);
-          dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
-          dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
-        }
-        // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the
-        // region, i.e. over the first 16 columns it loaded itself, never over
-        // columns another warpgroup still has to read.
-        ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
-        ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
-        if (sc == 0) {
-          // P^T / dS^T of this warpgroup's first 16 queries are in TMEM: dV / dK may start on them
-          ptx::tmem_wait_st();
-          ptx::tc_fence_before();
-          ptx::mbar_arrive(&ctl->pds_half);
-        }
-        // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
-        uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          const int chunk = ((col & 63) >> 3) + ch;
-          *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
-        }
-      }
-      ptx::tmem_wait_st();
-      ptx::fence_proxy_async_smem();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(&ctl->pds_full);
-      if (wg == 0 && n + 1 < n_steps) {
-        store_vec(n + 1, ln, dn);
-        ptx::mbar_arrive(&ctl->vec_full[(n + 1) & 1]);
-      }
-      // dQ: of the previous step while this step's MMAs run (kPipe), else of this step
-      if (kPipe) {
-        if (wg < 2 && n >= 1) read_out_dq(n - 1);
-      } else {
-        read_out_dq(n);
-      }
-    }
-    if (kPipe && n_steps > 0 && wg < 2) read_out_dq(n_steps - 1);
-    if (r == 0) ptx::bulk_wait_all();
-
-    // dV (warpgroup 0) and dK (warpgroup 1) of this key tile
-    T* out = nullptr;
-    if (wg == 0 && a.dv)
-      out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
-    if (wg == 1 && a.dk)
-      out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
-    if (wg >= 2) {
-      // warpgroups 2 and 3 have nothing to write
-    } else if (n_steps > 0) {
-      if (ok) ok = ptx::mbar_wait(&ctl->acc_full, 0, abort_flag);
-      ptx::tc_fence_after();
-      const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
-#pragma unroll 1
-      for (int cc = 0; cc < D / 32; ++cc) {
+      // D = 128: dQ of step n shares region A with S^T, so the four compute warpgroups move it out themselves
+      // (32 columns each) before the next step's S^T may be issued
+      auto read_out_dq = [&](int n) {
+        const uint32_t g = g0 + n;
+        const int h = hk * group + n / per_head;
+        const int q0 = (qt_begin + n % per_head) * BQ;
+        if (ok) ok = ptx::mbar_wait(&ctl->dq_full[0], g & 1, abort_flag);
+        ptx::tc_fence_after();
         uint32_t v[32];
-        ptx::tmem_ld32(src + cc * 32, v);
+        ptx::tmem_ld32(tdQ(g) + lane_addr + wg * 32, v);
         ptx::tmem_wait_ld();
-        if (ok && out && kv_row < a.Skv) {
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->dq_free[0]);
+        uint8_t* stage = sdq + wg * (BQ * 128);
+        if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging tile
+        ptx::named_barrier(3 + wg, BM);
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-            w.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-            w.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-            w.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-            *reinterpret_cast<uint4*>(out + cc * 32 + i) = w;
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
+              make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+        ptx::fence_proxy_async_smem();
+        ptx::named_barrier(3 + wg, BM);
+        if (r == 0 && ok) {
+          ptx::tma_reduce_add_4d(&tmdQ, stage, wg * 32, q0, h, b);
+          ptx::bulk_commit();
+        }
+      };
+
+      for (int n = 0; n < n_steps; ++n) {
+        const uint32_t g = g0 + n;
+        const int q0 = (qt_begin + n % per_head) * BQ;
+        // per-query vectors of the step, written by the producer warp: [0,128) -lse * log2(e), [128,256) -delta * scale
+        const float* vec = svec + (g & 1) * 2 * BQ;
+        uint8_t* ds_tile = sdS + (g % C::NDS) * C::kDsBytes;
+        // all threads reach this point every step, expired waits included
+        if (ok) ok = ptx::mbar_wait(&ctl->vec_full[g & 1], (g >> 1) & 1, abort_flag);
+        if (ok) ok = ptx::mbar_wait(&ctl->sp_full, g & 1, abort_flag);
+        ptx::tc_fence_after();
+        const bool diag = a.causal && q0 + shift < kv0 + BM;  // some (query, key) pairs of this step are masked
+        const bool masked = diag || kv0 + BM > kv_len;
+#pragma unroll
+        for (int sc = 0; sc < 2; ++sc) {
+          const int col = wg * 32 + sc * 16;  // 16 queries of the step
+          uint32_t s[16], dp[16];
+          ptx::tmem_ld16(tA + lane_addr + col, s);
+          ptx::tmem_ld16(tB + lane_addr + col, dp);
+          ptx::tmem_wait_ld();
+          uint32_t pk[8], dk[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(vec + col + i);
+            const float4 d4 = *reinterpret_cast<const float4*>(vec + BQ + col + i);
+            // P = 2^(c*s - lse2), dS = P * (scale*dP - scale*delta), in packed fp32 pairs
+            float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v,
+                                  make_float2(l4.x, l4.y));
+            float2 x1 = ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v,
+                                  make_float2(l4.z, l4.w));
+            if constexpr (GEN) {
+              if (a.mask.ptr && kv_row < a.Skv) {
+                // the mask element of (query, this thread's key): adjacent threads read adjacent keys
+                const int q = q0 + col + i;
+                const int64_t mo = b * a.mask.sb + (hk * group + n / per_head) * a.mask.sh + q * a.mask.sl + kv_row;
+                if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, mo);
+                if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, mo + a.mask.sl);
+                if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, mo + 2 * a.mask.sl);
+                if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, mo + 3 * a.mask.sl);
+              }
+            }
+            // (one exponential in eight on the FMA pipe: the 16 compute warps saturate the MUFU units in this phase;
+            // one in four is as fast within half a percent, three in eight and more are slower again)
+            float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), (i & 4) ? ptx::ex2_fma(x1.y) : ptx::ex2(x1.y));
+            if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
+              const int q = q0 + col + i + shift;
+              if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
+              if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
+              if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
+              if (!row_valid || (diag && q + 3 < kv_row)) p1.y = 0.f;
+            }
+            const float2 g0 = ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2,
+                                        make_float2(d4.x, d4.y));
+            const float2 g1 = ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2,
+                                        make_float2(d4.z, d4.w));
+            const float2 ds0 = ptx::mul2(p0, g0), ds1 = ptx::mul2(p1, g1);
+            pk[(i >> 1) + 0] = pack2<BF16>(p0.x, p0.y);
+            pk[(i >> 1) + 1] = pack2<BF16>(p1.x, p1.y);
+            dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
+            dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
+          }
+          // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the
+          // region, i.e. over the first 16 columns it loaded itself, never over
+          // columns another warpgroup still has to read.
+          ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
+          ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
+          if (sc == 0) {
+            // P^T / dS^T of this warpgroup's first 16 queries are in TMEM: dV / dK may start on them
+            ptx::tmem_wait_st();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&ctl->pds_half);
+          }
+          // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
+          uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            const int chunk = ((col & 63) >> 3) + ch;
+            *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
+                make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
+          }
+        }
+        ptx::tmem_wait_st();
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->pds_full);
+        if constexpr (!kPipe) read_out_dq(n);
+      }
+      g0 += n_steps;
+
+      if constexpr (!kPipe) {
+        // dV (warpgroup 0) and dK (warpgroup 1) of this key tile; the other warpgroups go on to the next item
+        if (wg < 2) {
+          T* out = nullptr;
+          if (wg == 0 && a.dv)
+            out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
+          if (wg == 1 && a.dk)
+            out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
+          if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
+          ptx::tc_fence_after();
+          const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t v[32];
+            ptx::tmem_ld32(src + cc * 32, v);
+            ptx::tmem_wait_ld();
+            if (cc == D / 32 - 1) {
+              // the accumulators may be overwritten by the next item's first products
+              ptx::tc_fence_before();
+              ptx::mbar_arrive(&ctl->acc_free);
+            }
+            if (ok && out && kv_row < a.Skv) store_acc_row(out + cc * 32, v);
           }
         }
       }
-    } else if (out && kv_row < a.Skv) {
-      // no query sees this key tile: zero gradients
-#pragma unroll
-      for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(out + i) = make_uint4(0, 0, 0, 0);
+    }
+    if constexpr (!kPipe) {
+      if (r == 0) ptx::bulk_wait_all();
     }
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 17) {
+  if (warp == C::kIssWarp) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+  if (tid == 0 && ctl->abort_flag && a.status) atomicOr(a.status, kStatusWaitExpired);
+}
+
+// ------------------------------------------------------------------ D = 64 --
+// With 64 columns per head there is room to take the step apart in time.  The 128 queries of a step are two
+// halves of 64 (compute warpgroups 0, 1 and 2, 3); S^T / dP^T of a half are MMAs with N = 64 into that half's
+// columns of regions A and B.  The issuer alternates between the halves: when the first half's P^T / dS^T are
+// ready it issues their dV / dK products and at once that half's S^T / dP^T of the NEXT step, then the same for
+// the second half, then the step's dQ.  So one half's element-wise phase runs while the tensor pipe works for
+// the other, instead of the pipe and the compute warps waiting for each other in turn.  A fifth warpgroup moves
+// the results out of TMEM (dQ of every step through one staging box and TMA reductions, dV / dK of an item
+// between its last two dQ); the producer warp also fetches the per-query vectors.  Shared memory: two K
+// buffers (the next item's first products are issued before this item's last dQ has read K), one V buffer (V is
+// last read a step before the item ends), three Q / dO stages (a stage is in use for a step and a half),
+// two dS^T tiles, one staging box.
+struct __align__(8) Ctl64 {
+  uint64_t item_full[2], item_empty[2];
+  uint64_t k_full[2], k_empty[2], v_full, v_empty;
+  uint64_t q_full[3], q_empty[3];
+  uint64_t vec_full[2];         // per-query vectors of a step (buffer g & 1), written by the producer warp
+  uint64_t vec_free[2];         // ... and read by every compute thread
+  uint64_t sp_full[2], pds[2];  // per half: S^T / dP^T are in TMEM; P^T / dS^T have been formed
+  uint64_t dq_full[2], dq_free[2];
+  uint64_t acc_full, acc_free;
+  int item[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct Cfg64 {
+  static constexpr int D = 64, TB = BM * D * 2, NQ = 3;
+  static constexpr int kDsBytes = BM * BQ * 2, kBox = BQ * 128;
+  static constexpr int oK = 0, oV = 2 * TB, oQ = 3 * TB, odO = oQ + NQ * TB, odS = odO + NQ * TB,
+                       oDq = odS + 2 * kDsBytes, oVec = oDq + kBox, oCtl = oVec + 2 * 2 * BQ * 4;
+  static constexpr int kSmem = oCtl + 256;
+  static_assert(sizeof(Ctl64) <= 256, "control block");
+  static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
+  // warps: 16 compute, 4 drain, producer, issuer, 2 idle (register reallocation works on whole warpgroups)
+  static constexpr int kProdWarp = 20, kIssWarp = 21, kThreads = 768;
+  static constexpr int kHalfThreads = 2 * BM;  // compute threads of one half of the queries
+};
+
+// P^T and dS^T of 16 queries for this thread's key row, as packed 16-bit pairs.  s / dp: S^T and dP^T (fp32
+// bits); lse2 / dsc: -lse * log2(e) and -delta * scale of the 16 queries; q_first: index of the first query;
+// mo: offset of (first query, this key) in the mask.
+template <bool BF16, bool GEN, typename T>
+__device__ __forceinline__ void p_ds_chunk(const BwdArgs& a, const uint32_t (&s)[16], const uint32_t (&dp)[16],
+                                           const float* lse2, const float* dsc, float2 c2v, float2 sc2, bool masked,
+                                           bool diag, bool row_valid, int kv_row, int q_first, int shift, int64_t mo,
+                                           uint32_t (&pk)[8], uint32_t (&dk)[8]) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i);
+    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
+    // P = 2^(c*s - lse2), dS = P * (scale*dP - scale*delta), in packed fp32 pairs
+    float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v, make_float2(l4.x, l4.y));
+    float2 x1 =
+        ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v, make_float2(l4.z, l4.w));
+    if constexpr (GEN) {
+      if (a.mask.ptr && kv_row < a.Skv) {
+        // the mask element of (query, this thread's key): adjacent threads read adjacent keys
+        const int q = q_first + i;
+        const int64_t m = mo + static_cast<int64_t>(i) * a.mask.sl;
+        if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, m);
+        if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, m + a.mask.sl);
+        if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, m + 2 * a.mask.sl);
+        if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, m + 3 * a.mask.sl);
+      }
+    }
+    // (one exponential in eight on the FMA pipe: the compute warps saturate the MUFU units in this phase)
+    float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y));
+    float2 p1 = make_float2(ptx::ex2(x1.x), (i & 4) ? ptx::ex2_fma(x1.y) : ptx::ex2(x1.y));
+    if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
+      const int q = q_first + i + shift;
+      if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
+      if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
+      if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
+      if (!row_valid || (diag && q + 3 < kv_row)) p1.y = 0.f;
+    }
+    const float2 g0 =
+        ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2, make_float2(d4.x, d4.y));
+    const float2 g1 =
+        ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2, make_float2(d4.z, d4.w));
+    const float2 ds0 = ptx::mul2(p0, g0), ds1 = ptx::mul2(p1, g1);
+    pk[(i >> 1) + 0] = pack2<BF16>(p0.x, p0.y);
+    pk[(i >> 1) + 1] = pack2<BF16>(p1.x, p1.y);
+    dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
+    dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
+  }
+}
+
+template <bool BF16, bool GEN>
+__global__ void __launch_bounds__(Cfg64::kThreads, 1)
+    bwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const __grid_constant__ CUtensorMap tmdQ, const BwdArgs a) {
+  using C = Cfg64;
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  constexpr int D = C::D, TB = C::TB, NQ = C::NQ;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((ptx::smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && a.status) atomicOr(a.status, kStatusBadSmemAlign);
+    return;
+  }
+  uint8_t* sK = smem + C::oK;    // 2 buffers
+  uint8_t* sV = smem + C::oV;
+  uint8_t* sQ = smem + C::oQ;    // NQ stages
+  uint8_t* sdO = smem + C::odO;  // NQ stages
+  uint8_t* sdS = smem + C::odS;  // 2 x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
+  uint8_t* sdq = smem + C::oDq;  // dQ staging box: [128 queries][32 floats], swizzled
+  float* svec = reinterpret_cast<float*>(smem + C::oVec);  // [2 buffers][lse2 | delta][128]
+  Ctl64* ctl = reinterpret_cast<Ctl64*>(smem + C::oCtl);
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Work items (a key tile of one (batch, kv head)) are drawn from a counter: heads in order and, within a
+  // head, the key tiles in order (under the causal mask the first key tile is seen by every query tile and walks
+  // longest).  Only the last `tail_heads` heads are ordered key tile by key tile ACROSS those heads, so that the
+  // items drawn last are the short ones and the CTAs finish together.
+  const int group = a.Hq / a.Hkv;
+  const int n_kt = (a.Skv + BM - 1) / BM, n_heads = a.Hkv * a.B;
+  const int n_items = n_kt * n_heads;
+  const int n_q_tiles = (a.Lq + BQ - 1) / BQ;
+  struct Item {
+    int hk, b, kv0, kv_len, shift, qt_begin, per_head, n_steps;
+  };
+  auto decode_item = [&](int w) {
+    Item it;
+    const int w0 = (n_heads - a.tail_heads) * n_kt;
+    int bh, nt;
+    if (w < w0) {
+      bh = w / n_kt;
+      nt = w - bh * n_kt;
+    } else {
+      const int x = w - w0;
+      nt = x / a.tail_heads;
+      bh = n_heads - a.tail_heads + (x - nt * a.tail_heads);
+    }
+    it.b = bh / a.Hkv, it.hk = bh - it.b * a.Hkv;
+    it.kv0 = nt * BM;
+    int kv_len = a.Skv;
+    if (a.kv_lens) {
+      int l = a.kv_lens[it.b];
+      kv_len = l < 0 ? 0 : (l < a.Skv ? l : a.Skv);
+    }
+    it.kv_len = kv_len;
+    it.shift = GEN ? causal_shift(a.causal, kv_len, a.Lq) : 0;  // key j participates iff j <= i + shift
+    // BM == BQ: query tiles before the key tile see none of it (general: first tile with a row i >= kv0 - shift)
+    it.qt_begin = a.causal ? (GEN ? (it.kv0 - it.shift > 0 ? (it.kv0 - it.shift) / BQ : 0) : nt) : 0;
+    it.per_head = (it.kv0 < kv_len && it.qt_begin < n_q_tiles) ? n_q_tiles - it.qt_begin : 0;
+    it.n_steps = it.per_head * group;
+    return it;
+  };
+
+  if (warp == C::kProdWarp && lane == 0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&ctl->item_full[i], 1);
+      ptx::mbar_init(&ctl->item_empty[i], 1 + kCompute + BM);  // issuing lane, compute threads, drain threads
+      ptx::mbar_init(&ctl->k_full[i], 1);
+      ptx::mbar_init(&ctl->k_empty[i], 1);
+      ptx::mbar_init(&ctl->vec_full[i], 32);  // the lanes of the producer warp
+      ptx::mbar_init(&ctl->vec_free[i], kCompute);
+      ptx::mbar_init(&ctl->sp_full[i], 1);
+      ptx::mbar_init(&ctl->pds[i], C::kHalfThreads);
+      ptx::mbar_init(&ctl->dq_full[i], 1);
+      ptx::mbar_init(&ctl->dq_free[i], BM);
+    }
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      ptx::mbar_init(&ctl->q_full[i], 1);
+      ptx::mbar_init(&ctl->q_empty[i], 1);
+    }
+    ptx::mbar_init(&ctl->v_full, 1);
+    ptx::mbar_init(&ctl->v_empty, 1);
+    ptx::mbar_init(&ctl->acc_full, 1);
+    ptx::mbar_init(&ctl->acc_free, BM);
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::tma_prefetch_desc(&tmQ);
+    ptx::tma_prefetch_desc(&tmK);
+    ptx::tma_prefetch_desc(&tmV);
+    ptx::tma_prefetch_desc(&tmdO);
+    ptx::tma_prefetch_desc(&tmdQ);
+  }
+  if (warp == C::kIssWarp) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  const uint32_t tA = tmem;         // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w); half h: cols [64h, 64h+64)
+  const uint32_t tB = tmem + 128;   // dP^T -> dS^T, likewise
+  const uint32_t tdV = tmem + 256;  // 64 columns
+  const uint32_t tdK = tmem + 320;  // 64 columns
+  auto tdQ = [&](uint32_t g) { return tmem + 384 + (g & 1) * D; };  // dQ of running step g
+
+  // Every role walks the same sequence of items and, within an item, of steps; g counts the steps over all
+  // items of this CTA (per-step barriers and buffers go by it), k the items (per-item barriers).
+  if (warp >= 20) {
+    // (96 registers for the 512 compute threads, 48 for the other 256: together the 80 x 768 the CTA was
+    // launched with, so the increase can always be served)
+    ptx::setmaxnreg_dec<48>();
+    if (warp == C::kProdWarp) {
+      // ------------------------------------------------------------ producer --
+      // Lane 0 draws the items, publishes those with steps to the other warps and feeds their tiles by TMA; the
+      // whole warp fetches the per-query vectors of every step (-lse * log2(e) and -delta * scale).  A key tile
+      // that no query sees has no steps: the warp writes its zero gradients here and nobody else hears of it
+      // (so a run of such items cannot fill the two-slot queue while the issuer looks one item ahead).
+      uint32_t gq = 0;  // steps of earlier items
+      bool dep_waited = false;
+      for (uint32_t i = 0;;) {  // i: items published so far
+        int w = 0;
+        if (lane == 0) {
+          w = atomicAdd(a.sched, 1);
+          if (w >= n_items) w = -1;
+        }
+        w = __shfl_sync(0xffffffffu, w, 0);
+        Item it = {};
+        if (w >= 0) {
+          it = decode_item(w);
+          if (it.n_steps == 0) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              void* base = t == 0 ? a.dv : a.dk;
+              const Str3& st = t == 0 ? a.dvs : a.dks;
+              if (!base) continue;
+              T* out = reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h;
+              for (int e = lane; e < BM * (D / 8); e += 32) {
+                const int row = it.kv0 + e / (D / 8);
+                if (row < a.Skv)
+                  *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * st.s + (e % (D / 8)) * 8) =
+                      make_uint4(0, 0, 0, 0);
+              }
+            }
+            continue;
+          }
+        }
+        int ok = 1;
+        if (lane == 0) {
+          const int slot = i & 1;
+          ok = ptx::mbar_wait(&ctl->item_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
+          if (ok) {
+            ctl->item[slot] = w;
+            ptx::mbar_arrive(&ctl->item_full[slot]);
+          }
+          if (ok && w >= 0) {
+            // the MMAs that read this K buffer (two items ago) / V (the item before) have completed
+            ok = ptx::mbar_wait(&ctl->k_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
+            if (ok) {
+              ptx::mbar_arrive_expect_tx(&ctl->k_full[slot], TB);
+              ptx::tma_load_4d(sK + slot * TB, &tmK, &ctl->k_full[slot], 0, it.kv0, it.hk, it.b);
+              ok = ptx::mbar_wait(&ctl->v_empty, (i & 1) ^ 1, abort_flag);
+            }
+            if (ok) {
+              ptx::mbar_arrive_expect_tx(&ctl->v_full, TB);
+              ptx::tma_load_4d(sV, &tmV, &ctl->v_full, 0, it.kv0, it.hk, it.b);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok || w < 0) break;
+        for (int n = 0; n < it.n_steps; ++n) {
+          const uint32_t g = gq + n;
+          const int st = g % NQ;
+          const int h = it.hk * group + n / it.per_head;
+          const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+          if (lane == 0) {
+            ok = ptx::mbar_wait(&ctl->q_empty[st], ((g / NQ) & 1) ^ 1, abort_flag);
+            if (ok) {
+              ptx::mbar_arrive_expect_tx(&ctl->q_full[st], 2 * TB);
+              ptx::tma_load_4d(sQ + st * TB, &tmQ, &ctl->q_full[st], 0, q0, h, it.b);
+              ptx::tma_load_4d(sdO + st * TB, &tmdO, &ctl->q_full[st], 0, q0, h, it.b);
+            }
+            // The vectors' buffer was last read in step g - 2.  (A barrier per buffer: it cannot complete its next
+            // phase before this warp has written the buffer again, so the parity below is never ambiguous, as it
+            // would be on a barrier that advances every step while this warp is held up at an item boundary.)
+            if (ok && g >= 2) ok = ptx::mbar_wait(&ctl->vec_free[g & 1], ((g >> 1) - 1) & 1, abort_flag);
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          if (!dep_waited) {
+            // This kernel is launched early behind the delta pre-pass: barriers, TMEM and the loads above need
+            // only the inputs; delta is first read here.
+            ptx::grid_dep_wait();
+            dep_waited = true;
+          }
+          float lv[4], dl[4];
+          const int64_t base = (static_cast<int64_t>(it.b) * a.Hq + h) * a.Lq + q0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = j * 32 + lane;
+            lv[j] = -INFINITY;  // rows beyond Lq behave like rows without any participating key: P = 0
+            dl[j] = 0.f;
+            if (q0 + row < a.Lq) {
+              lv[j] = a.lse[base + row];
+              dl[j] = a.delta[base + row];
+            }
+          }
+          float* nv = svec + (g & 1) * 2 * BQ;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = j * 32 + lane;
+            nv[row] = lv[j] == -INFINITY ? -INFINITY : -lv[j] * kLog2e;
+            nv[BQ + row] = -dl[j] * a.scale;
+          }
+          ptx::mbar_arrive(&ctl->vec_full[g & 1]);
+        }
+        if (!ok) break;
+        gq += it.n_steps;
+        ++i;
+      }
+    } else if (warp == C::kIssWarp) {
+      // -------------------------------------------------------------- issuer --
+      // The whole warp runs the loop (waits made uniform by a vote); one elected lane issues, so that addresses
+      // and descriptors stay warp-uniform.
+      const bool leader = ptx::elect_one();
+      auto uwait = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
+      };
+      constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
+      const uint32_t fmt = BF16 ? 1 : 0;
+      const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ / 2, fmt, 0, 0);  // S^T, dP^T of a half: N = 64 queries
+      const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);     // dV, dK: A from TMEM, B MN-major
+      const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);      // dQ: both operands MN-major
+      const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
+      uint32_t fi = 0;  // items taken from the queue
+      // the next item, or false: none is left or a wait ran out
+      auto fetch = [&](Item& it) {
+        const int slot = fi & 1;
+        if (!uwait(&ctl->item_full[slot], (fi >> 1) & 1)) return false;
+        const int w = ctl->item[slot];
+        __syncwarp();  // every lane has read the slot
+        if (leader) ptx::mbar_arrive(&ctl->item_empty[slot]);
+        ++fi;
+        if (w < 0) return false;
+        it = decode_item(w);
+        return true;
+      };
+      // K and V of the k-th item of this CTA are in shared memory
+      auto kv_ready = [&](uint32_t k) {
+        return uwait(&ctl->k_full[k & 1], (k >> 1) & 1) && uwait(&ctl->v_full, k & 1);
+      };
+      auto q_ready = [&](uint32_t g) {
+        const bool ok = uwait(&ctl->q_full[g % NQ], (g / NQ) & 1);
+        ptx::tc_fence_after();
+        return ok;
+      };
+      // S^T = K Q^T and dP^T = V dO^T of half h of running step g, on the tiles of the CTA's k-th item
+      auto issue_s_dp = [&](uint32_t g, uint32_t k, int h) {
+        const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ + (g % NQ) * TB + h * (TB / 2)), 16);
+        const uint32_t dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO + (g % NQ) * TB + h * (TB / 2)), 16);
+        const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK + (k & 1) * TB), 16);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          if (leader) ptx::mma_ss2(tA + h * 64, klo + ks * 2, kHi, qlo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          if (leader) ptx::mma_ss2(tB + h * 64, vlo + ks * 2, kHi, dolo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
+        if (leader) ptx::mma_commit(&ctl->sp_full[h]);
+      };
+      Item cur = {}, nxt = {};
+      uint32_t g = 0, k = 0;
+      bool have = fetch(cur);
+      bool ok = have && kv_ready(0) && q_ready(0);
+      if (ok) {
+        issue_s_dp(0, 0, 0);
+        issue_s_dp(0, 0, 1);
+        if (cur.n_steps == 1 && leader) ptx::mma_commit(&ctl->v_empty);
+      }
+      while (have && ok) {
+        bool have_next = false;
+        for (int n = 0; n < cur.n_steps && ok; ++n, ++g) {
+          const bool last = n + 1 == cur.n_steps;
+          const int st = g % NQ;
+          const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), kHalfBytes);
+          const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), kHalfBytes);
+          bool next_step = false;  // there is a step g + 1 (of this item or the next)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (!(ok = uwait(&ctl->pds[h], g & 1))) break;
+            // the first products of an item overwrite the accumulators: the item before has been read out
+            if (h == 0 && n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
+            ptx::tc_fence_after();
+            // dV and dK contract over the queries, 16 per k-step (2048 bytes of B); half h holds k-steps 4h .. 4h+3
+#pragma unroll
+            for (int ks = 4 * h; ks < 4 * h + 4; ++ks)
+              if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+                           (n > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+            for (int ks = 4 * h; ks < 4 * h + 4; ++ks)
+              if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+                           (n > 0 || ks > 0) ? 1u : 0u);
+            if (h == 0) {
+              if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
+              next_step = ok && (!last || have_next);
+              if (next_step) ok = q_ready(g + 1);
+              if (!ok) break;
+            } else {
+              // Q and dO of this step have been read, and with these products the step's vectors; after the
+              // item's last step dV and dK are complete
+              if (leader) ptx::mma_commit(&ctl->q_empty[st]);
+              if (last && leader) ptx::mma_commit(&ctl->acc_full);
+            }
+            // P^T / dS^T of this half have been consumed from TMEM (in issue order): the half's S^T / dP^T of
+            // the next step go in at once
+            if (next_step) issue_s_dp(g + 1, last ? k + 1 : k, h);
+          }
+          if (!ok) break;
+          if (next_step) {
+            // V is free once dP^T of the last step of its item has been issued
+            const int n_of = last ? nxt.n_steps : cur.n_steps, idx = last ? 0 : n + 1;
+            if (idx + 1 == n_of && leader) ptx::mma_commit(&ctl->v_empty);
+          }
+          if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
+          const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (g & 1) * C::kDsBytes), kHalfBytes);
+          const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK + (k & 1) * TB), kHalfBytes);
+#pragma unroll
+          for (int ks = 0; ks < BM / 16; ++ks)  // contraction over the 128 keys
+            if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_commit(&ctl->dq_full[g & 1]);
+          // every MMA of the item has been issued: its K buffer goes back
+          if (last && leader) ptx::mma_commit(&ctl->k_empty[k & 1]);
+        }
+        cur = nxt;
+        have = have_next;
+        ++k;
+      }
+    }
+  } else if (warp >= 16) {
+    // ----------------------------------------------------------------- drain --
+    // dQ of every step (thread r = query row r; 32 columns at a time through the swizzled staging box and a TMA
+    // reduction: coalesced, rows beyond Lq are clipped by the tensor map), and dV / dK of the item (thread r =
+    // key row r, written directly) between the last two dQ.
+    ptx::setmaxnreg_dec<48>();
+    const int r = tid & (BM - 1);
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    bool ok = true;
+    ptx::grid_dep_wait();  // the reductions below need the dQ accumulator cleared by the pre-pass
+    uint32_t g = 0;
+    for (uint32_t k = 0;; ++k) {
+      const int slot = k & 1;
+      if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
+      const int w = ok ? ctl->item[slot] : -1;
+      ptx::mbar_arrive(&ctl->item_empty[slot]);
+      // the warpgroup leaves as one (its named barriers count all 128 threads) when any of its waits ran out
+      if (ptx::named_barrier_or(1, BM, !ok)) break;
+      if (w < 0) break;
+      const Item it = decode_item(w);
+      for (int n = 0; n < it.n_steps; ++n, ++g) {
+        if (n + 1 == it.n_steps) {
+          // dV, then dK: complete once the last step's products are (before its dQ)
+          if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
+          ptx::tc_fence_after();
+          const int kv_row = it.kv0 + r;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            void* base = t == 0 ? a.dv : a.dk;
+            const Str3& st = t == 0 ? a.dvs : a.dks;
+            T* out = base ? reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h + static_cast<int64_t>(kv_row) * st.s
+                          : nullptr;
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t v[32];
+              ptx::tmem_ld32((t == 0 ? tdV : tdK) + lane_addr + cc * 32, v);
+              ptx::tmem_wait_ld();
+              if (t == 1 && cc == D / 32 - 1) {
+                // the accumulators may be overwritten by the next item's first products
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(&ctl->acc_free);
+              }
+              if (ok && out && kv_row < a.Skv) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 w4;
+                  w4.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+                  w4.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                  w4.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                  w4.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                  *reinterpret_cast<uint4*>(out + cc * 32 + i) = w4;
+                }
+              }
+            }
+          }
+        }
+        const int h = it.hk * group + n / it.per_head;
+        const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+        if (ok) ok = ptx::mbar_wait(&ctl->dq_full[g & 1], (g >> 1) & 1, abort_flag);
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t v[32];
+          ptx::tmem_ld32(tdQ(g) + lane_addr + cc * 32, v);
+          ptx::tmem_wait_ld();
+          if (cc == D / 32 - 1) {
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&ctl->dq_free[g & 1]);
+          }
+          if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging box
+          ptx::named_barrier(1, BM);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(sdq + r * 128 + ((ch ^ (r & 7)) << 4)) =
+                make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+          ptx::fence_proxy_async_smem();
+          ptx::named_barrier(1, BM);
+          if (r == 0 && ok) {
+            ptx::tma_reduce_add_4d(&tmdQ, sdq, cc * 32, q0, h, it.b);
+            ptx::bulk_commit();
+          }
+        }
+      }
+    }
+    if (r == 0) ptx::bulk_wait_all();
+  } else {
+    // --------------------------------------------------------------- compute --
+    ptx::setmaxnreg_inc<96>();
+    const int wg = warp >> 2;      // which 32 queries of every step
+    const int half = wg >> 1;      // which half of the step
+    const int r = tid & (BM - 1);  // key row within the tile
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const float c = a.scale * kLog2e;
+    const float2 c2v = make_float2(c, c), sc2 = make_float2(a.scale, a.scale);
+    bool ok = true;
+    ptx::grid_dep_launch();  // (the conversion kernel may come up; it waits for this grid)
+    uint32_t g = 0;
+    for (uint32_t k = 0;; ++k) {
+      const int slot = k & 1;
+      if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
+      const int w = ok ? ctl->item[slot] : -1;
+      ptx::mbar_arrive(&ctl->item_empty[slot]);
+      if (w < 0) break;
+      const Item it = decode_item(w);
+      const int kv_row = it.kv0 + r;
+      const bool row_valid = kv_row < it.kv_len;
+      for (int n = 0; n < it.n_steps; ++n, ++g) {
+        const int hq = it.hk * group + n / it.per_head;
+        const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+        const float* vec = svec + (g & 1) * 2 * BQ;
+        uint8_t* ds_tile = sdS + (g & 1) * C::kDsBytes;
+        if (ok) ok = ptx::mbar_wait(&ctl->vec_full[g & 1], (g >> 1) & 1, abort_flag);
+        if (ok) ok = ptx::mbar_wait(&ctl->sp_full[half], g & 1, abort_flag);
+        ptx::tc_fence_after();
+        const bool diag = a.causal && q0 + it.shift < it.kv0 + BM;  // some (query, key) pairs of this step are masked
+        const bool masked = diag || it.kv0 + BM > it.kv_len;
+#pragma unroll
+        for (int sc = 0; sc < 2; ++sc) {
+          const int col = wg * 32 + sc * 16;  // 16 queries of the step
+          uint32_t s[16], dp[16];
+          ptx::tmem_ld16(tA + lane_addr + col, s);
+          ptx::tmem_ld16(tB + lane_addr + col, dp);
+          ptx::tmem_wait_ld();
+          uint32_t pk[8], dk[8];
+          int64_t mo = 0;
+          if constexpr (GEN)
+            mo = it.b * a.mask.sb + hq * a.mask.sh + static_cast<int64_t>(q0 + col) * a.mask.sl + kv_row;
+          p_ds_chunk<BF16, GEN, T>(a, s, dp, vec + col, vec + BQ + col, c2v, sc2, masked, diag, row_valid, kv_row,
+                                   q0 + col, it.shift, mo, pk, dk);
+          // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the region, i.e. over the first 16
+          // columns it loaded itself, never over columns another warpgroup still has to read.
+          ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
+          ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
+          // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
+          uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            const int chunk = ((col & 63) >> 3) + ch;
+            *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
+                make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
+          }
+        }
+        ptx::mbar_arrive(&ctl->vec_free[g & 1]);
+        ptx::tmem_wait_st();
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->pds[half]);
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == C::kIssWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
@@ -561,15 +1373,20 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
       !make_map_f32(&tdq, a.dq_accum, D, a.Lq, a.Hq, a.B))
     return cudaErrorInvalidValue;
   cudaError_t e;  // (dq_accum has been cleared by the delta pre-pass)
-  auto kern = bwd_tc_kernel<D, BF16, GEN>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmem);
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, BwdArgs);
+  if constexpr (D == 64) kern = bwd_tc64_kernel<BF16, GEN>;
+  else kern = bwd_tc_kernel<D, BF16, GEN>;
+  constexpr int kSmemBytes = D == 64 ? Cfg64::kSmem : Cfg<D>::kSmem;
+  constexpr int kBlock = D == 64 ? Cfg64::kThreads : Cfg<D>::kThreads;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_kt = (a.Skv + BM - 1) / BM;
-  const long long n_ctas = static_cast<long long>(n_kt) * a.Hkv * a.B;
-  if (n_ctas > 0x7fffffffll) return cudaErrorInvalidValue;
-  dim3 grid(static_cast<unsigned>(n_ctas));
+  const long long n_items = static_cast<long long>(n_kt) * a.Hkv * a.B;
+  if (n_items > 0x7fffffffll) return cudaErrorInvalidValue;
+  const int sms = sm_count(device);
+  dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));  // persistent: one CTA per SM
   BwdArgs ka = a;
-  // two waves' worth of heads at the end of the grid (one CTA per SM); only worth it where walks differ in length
+  // two waves' worth of heads at the end of the item order; only worth it where walks differ in length
   ka.tail_heads = 0;
   if (a.causal) {
     const long long heads = static_cast<long long>(a.Hkv) * a.B;
@@ -581,8 +1398,8 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = Cfg<D>::kSmem;
+  cfg.blockDim = dim3(kBlock);
+  cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cfg.attrs = attr, cfg.numAttrs = 1;  // early launch behind the delta pre-pass
   e = cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tdo, tdq, ka);
@@ -612,7 +1429,11 @@ cudaError_t launch_g(int dtype, int D, const BwdArgs& a, int device, cudaStream_
 cudaError_t launch_bwd_tc(int dtype, int D, const BwdArgs& a, int device, cudaStream_t stream) {
   BwdArgs pre = a;
   pre.zero_dq_accum = 1;
-  cudaError_t e = launch_bwd_delta(dtype, D, pre, stream);
+  // The work counter starts at zero for every launch; cleared ahead of the pre-pass so that the kernel
+  // launched early behind the pre-pass already sees it.
+  cudaError_t e = cudaMemsetAsync(a.sched, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return e;
+  e = launch_bwd_delta(dtype, D, pre, stream);
   if (e != cudaSuccess) return e;
   const bool general = a.mask.ptr != nullptr || a.causal == TT_ATTN_CAUSAL_BOTTOM_RIGHT;
   return general ? launch_g<true>(dtype, D, a, device, stream) : launch_g<false>(dtype, D, a, device, stream);

@@ -61,8 +61,9 @@ struct BwdArgs {
   float* delta;     // workspace [B, Hq, Lq]
   float* dq_accum;  // workspace [B, Hq, Lq, D] fp32 (tensor-core path), zeroed by the delta pre-pass
   int zero_dq_accum;  // set by the tensor-core launcher: the delta kernel also clears dq_accum
-  int tail_heads;     // tensor-core kernel: (batch, kv head) pairs at the end of the grid whose key tiles are
+  int tail_heads;     // tensor-core kernel: (batch, kv head) pairs at the end of the item order whose key tiles are
                       // ordered longest walk first across heads (set by its launcher)
+  int* sched;         // tensor-core kernel: work counter in scratch memory, zeroed by its launcher
   void* dq;
   void* dk;
   void* dv;
