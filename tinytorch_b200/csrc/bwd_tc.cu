@@ -756,19 +756,21 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
 
 // ------------------------------------------------------------------ D = 64 --
 // With 64 columns per head there is room to take the step apart in time.  The 128 queries of a step are two
-// halves of 64 (compute warpgroups 0, 1 and 2, 3); S^T / dP^T of a half are MMAs with N = 64 into that half's
-// columns of regions A and B.  The issuer alternates between the halves: when the first half's P^T / dS^T are
-// ready it issues their dV / dK products and at once that half's S^T / dP^T of the NEXT step, then the same for
-// the second half, then the step's dQ.  So one half's element-wise phase runs while the tensor pipe works for
-// the other, instead of the pipe and the compute warps waiting for each other in turn.  A fifth warpgroup moves
-// the results out of TMEM (dQ of every step through one staging box and TMA reductions, dV / dK of an item
-// between its last two dQ); the producer warp also fetches the per-query vectors.  Shared memory: two K
-// buffers (the next item's first products are issued before this item's last dQ has read K), one V buffer (V is
-// last read a step before the item ends), three Q / dO stages (a stage is in use for a step and a half),
-// two dS^T tiles, one staging box.
+// halves of 64; S^T / dP^T of a half are MMAs with N = 64 into that half's columns of regions A and B.  All four
+// compute warpgroups work on one half at a time (16 queries each), then on the other, and the issuer alternates
+// likewise: when the first half's P^T / dS^T are ready it issues their dV / dK products and at once that half's
+// S^T / dP^T of the NEXT step; then the same for the second half, with the step's dQ in between.  So the
+// element-wise phase of one half runs while the tensor pipe works for the other, instead of the pipe and the
+// compute warps waiting for each other in turn.  A fifth warpgroup moves the results out of TMEM (each of its
+// warps the dQ of its 32 query rows through a staging box of its own and TMA reductions, and dV / dK of an
+// item between its last two dQ); the producer warp also fetches the per-query vectors.  Shared memory: two
+// K / V stages (the next item's first products are issued before this item's last dQ has read K), three Q / dO
+// stages (a stage is in use for two steps), dS^T as two blocks of 64 queries: two buffers for the first half
+// (the next step's is written while dQ reads this step's), one for the second (S^T / dP^T of the next step's
+// second half are issued behind dQ).
 struct __align__(8) Ctl64 {
   uint64_t item_full[2], item_empty[2];
-  uint64_t k_full[2], k_empty[2], v_full, v_empty;
+  uint64_t kv_full[2], kv_empty[2];
   uint64_t q_full[3], q_empty[3];
   uint64_t vec_full[2];         // per-query vectors of a step (buffer g & 1), written by the producer warp
   uint64_t vec_free[2];         // ... and read by every compute thread
@@ -782,30 +784,29 @@ struct __align__(8) Ctl64 {
 
 struct Cfg64 {
   static constexpr int D = 64, TB = BM * D * 2, NQ = 3;
-  static constexpr int kDsBytes = BM * BQ * 2, kBox = BQ * 128;
-  static constexpr int oK = 0, oV = 2 * TB, oQ = 3 * TB, odO = oQ + NQ * TB, odS = odO + NQ * TB,
-                       oDq = odS + 2 * kDsBytes, oVec = oDq + kBox, oCtl = oVec + 2 * 2 * BQ * 4;
+  static constexpr int kBlk = BM * 128;    // a dS^T block: 128 key rows x 64 queries
+  static constexpr int kBox = 32 * 128;    // a drain warp's staging box: 32 query rows x 32 floats
+  static constexpr int oKV = 0, oQ = 4 * TB, odO = oQ + NQ * TB, odS = odO + NQ * TB, oDq = odS + 3 * kBlk,
+                       oVec = oDq + 4 * kBox, oCtl = oVec + 2 * 2 * BQ * 4;
   static constexpr int kSmem = oCtl + 256;
   static_assert(sizeof(Ctl64) <= 256, "control block");
   static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
   // warps: 16 compute, 4 drain, producer, issuer, 2 idle (register reallocation works on whole warpgroups)
   static constexpr int kProdWarp = 20, kIssWarp = 21, kThreads = 768;
-  static constexpr int kHalfThreads = 2 * BM;  // compute threads of one half of the queries
 };
 
 // P^T and dS^T of 16 queries for this thread's key row, as packed 16-bit pairs.  s / dp: S^T and dP^T (fp32
 // bits); lse2 / dsc: -lse * log2(e) and -delta * scale of the 16 queries; q_first: index of the first query;
-// mo: offset of (first query, this key) in the mask.
+// mo: offset of (first query, this key) in the mask; n_hidden: how many of the 16 queries, from the first on,
+// do not see this key (causal triangle; all 16 for a key beyond kv_len).
 template <bool BF16, bool GEN, typename T>
-__device__ __forceinline__ void p_ds_chunk(const BwdArgs& a, const uint32_t (&s)[16], const uint32_t (&dp)[16],
-                                           const float* lse2, const float* dsc, float2 c2v, float2 sc2, bool masked,
-                                           bool diag, bool row_valid, int kv_row, int q_first, int shift, int64_t mo,
-                                           uint32_t (&pk)[8], uint32_t (&dk)[8]) {
+__device__ __forceinline__ void p_ds_chunk(const BwdArgs& a, uint32_t (&s)[16], const uint32_t (&dp)[16],
+                                           const float* lse2, const float* dsc, float2 c2v, float2 sc2, int n_hidden,
+                                           int kv_row, int q_first, int64_t mo, uint32_t (&pk)[8], uint32_t (&dk)[8]) {
+  // exponents c*s - lse2, in packed fp32 pairs, in place
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
     const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i);
-    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
-    // P = 2^(c*s - lse2), dS = P * (scale*dP - scale*delta), in packed fp32 pairs
     float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v, make_float2(l4.x, l4.y));
     float2 x1 =
         ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v, make_float2(l4.z, l4.w));
@@ -820,16 +821,24 @@ __device__ __forceinline__ void p_ds_chunk(const BwdArgs& a, const uint32_t (&s)
         if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, m + 3 * a.mask.sl);
       }
     }
+    s[i] = __float_as_uint(x0.x), s[i + 1] = __float_as_uint(x0.y);
+    s[i + 2] = __float_as_uint(x1.x), s[i + 3] = __float_as_uint(x1.y);
+  }
+  // Hidden pairs get P = 0 through the exponent.  (Kept apart from the arithmetic before and after, which then
+  // is the same straight-line code for every step; only the diagonal step and a ragged last key tile come here.)
+  if (n_hidden > 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n_hidden) s[i] = 0xff800000u;  // -inf
+  }
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
+    // P = 2^x, dS = P * (scale*dP - scale*delta)
     // (one exponential in eight on the FMA pipe: the compute warps saturate the MUFU units in this phase)
-    float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y));
-    float2 p1 = make_float2(ptx::ex2(x1.x), (i & 4) ? ptx::ex2_fma(x1.y) : ptx::ex2(x1.y));
-    if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
-      const int q = q_first + i + shift;
-      if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
-      if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
-      if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
-      if (!row_valid || (diag && q + 3 < kv_row)) p1.y = 0.f;
-    }
+    const float2 p0 = make_float2(ptx::ex2(__uint_as_float(s[i])), ptx::ex2(__uint_as_float(s[i + 1])));
+    const float2 p1 = make_float2(ptx::ex2(__uint_as_float(s[i + 2])),
+                                  (i & 4) ? ptx::ex2_fma(__uint_as_float(s[i + 3])) : ptx::ex2(__uint_as_float(s[i + 3])));
     const float2 g0 =
         ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2, make_float2(d4.x, d4.y));
     const float2 g1 =
@@ -855,12 +864,13 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
     if (threadIdx.x == 0 && a.status) atomicOr(a.status, kStatusBadSmemAlign);
     return;
   }
-  uint8_t* sK = smem + C::oK;    // 2 buffers
-  uint8_t* sV = smem + C::oV;
+  uint8_t* sKV = smem + C::oKV;  // 2 stages of [K tile | V tile]
   uint8_t* sQ = smem + C::oQ;    // NQ stages
   uint8_t* sdO = smem + C::odO;  // NQ stages
-  uint8_t* sdS = smem + C::odS;  // 2 x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
-  uint8_t* sdq = smem + C::oDq;  // dQ staging box: [128 queries][32 floats], swizzled
+  // dS^T, [128 key rows][64 queries] blocks with 128-byte swizzle: first half of step g in block g & 1, second
+  // half in block 2
+  uint8_t* sdS = smem + C::odS;
+  uint8_t* sdq = smem + C::oDq;  // dQ staging: per drain warp [32 queries][32 floats], swizzled
   float* svec = reinterpret_cast<float*>(smem + C::oVec);  // [2 buffers][lse2 | delta][128]
   Ctl64* ctl = reinterpret_cast<Ctl64*>(smem + C::oCtl);
   volatile int* abort_flag = &ctl->abort_flag;
@@ -910,12 +920,12 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&ctl->item_full[i], 1);
       ptx::mbar_init(&ctl->item_empty[i], 1 + kCompute + BM);  // issuing lane, compute threads, drain threads
-      ptx::mbar_init(&ctl->k_full[i], 1);
-      ptx::mbar_init(&ctl->k_empty[i], 1);
+      ptx::mbar_init(&ctl->kv_full[i], 1);
+      ptx::mbar_init(&ctl->kv_empty[i], 1);
       ptx::mbar_init(&ctl->vec_full[i], 32);  // the lanes of the producer warp
       ptx::mbar_init(&ctl->vec_free[i], kCompute);
       ptx::mbar_init(&ctl->sp_full[i], 1);
-      ptx::mbar_init(&ctl->pds[i], C::kHalfThreads);
+      ptx::mbar_init(&ctl->pds[i], kCompute);
       ptx::mbar_init(&ctl->dq_full[i], 1);
       ptx::mbar_init(&ctl->dq_free[i], BM);
     }
@@ -924,8 +934,6 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       ptx::mbar_init(&ctl->q_full[i], 1);
       ptx::mbar_init(&ctl->q_empty[i], 1);
     }
-    ptx::mbar_init(&ctl->v_full, 1);
-    ptx::mbar_init(&ctl->v_empty, 1);
     ptx::mbar_init(&ctl->acc_full, 1);
     ptx::mbar_init(&ctl->acc_free, BM);
     ctl->abort_flag = 0;
@@ -944,8 +952,10 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tA = tmem;         // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w); half h: cols [64h, 64h+64)
-  const uint32_t tB = tmem + 128;   // dP^T -> dS^T, likewise
+  // Regions A (S^T -> P^T) and B (dP^T -> dS^T): half h in columns [64h, 64h+64), warpgroup w's 16 queries of
+  // the half in [64h + 16w, +16); their 16-bit results go over the first 8 of those columns.
+  const uint32_t tA = tmem;
+  const uint32_t tB = tmem + 128;
   const uint32_t tdV = tmem + 256;  // 64 columns
   const uint32_t tdK = tmem + 320;  // 64 columns
   auto tdQ = [&](uint32_t g) { return tmem + 384 + (g & 1) * D; };  // dQ of running step g
@@ -999,18 +1009,12 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
             ctl->item[slot] = w;
             ptx::mbar_arrive(&ctl->item_full[slot]);
           }
+          // the MMAs that read this stage (two items ago) have completed
+          if (ok && w >= 0) ok = ptx::mbar_wait(&ctl->kv_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
           if (ok && w >= 0) {
-            // the MMAs that read this K buffer (two items ago) / V (the item before) have completed
-            ok = ptx::mbar_wait(&ctl->k_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
-            if (ok) {
-              ptx::mbar_arrive_expect_tx(&ctl->k_full[slot], TB);
-              ptx::tma_load_4d(sK + slot * TB, &tmK, &ctl->k_full[slot], 0, it.kv0, it.hk, it.b);
-              ok = ptx::mbar_wait(&ctl->v_empty, (i & 1) ^ 1, abort_flag);
-            }
-            if (ok) {
-              ptx::mbar_arrive_expect_tx(&ctl->v_full, TB);
-              ptx::tma_load_4d(sV, &tmV, &ctl->v_full, 0, it.kv0, it.hk, it.b);
-            }
+            ptx::mbar_arrive_expect_tx(&ctl->kv_full[slot], 2 * TB);
+            ptx::tma_load_4d(sKV + slot * 2 * TB, &tmK, &ctl->kv_full[slot], 0, it.kv0, it.hk, it.b);
+            ptx::tma_load_4d(sKV + slot * 2 * TB + TB, &tmV, &ctl->kv_full[slot], 0, it.kv0, it.hk, it.b);
           }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -1078,7 +1082,6 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ / 2, fmt, 0, 0);  // S^T, dP^T of a half: N = 64 queries
       const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);     // dV, dK: A from TMEM, B MN-major
       const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);      // dQ: both operands MN-major
-      const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
       uint32_t fi = 0;  // items taken from the queue
       // the next item, or false: none is left or a wait ran out
       auto fetch = [&](Item& it) {
@@ -1093,9 +1096,7 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
         return true;
       };
       // K and V of the k-th item of this CTA are in shared memory
-      auto kv_ready = [&](uint32_t k) {
-        return uwait(&ctl->k_full[k & 1], (k >> 1) & 1) && uwait(&ctl->v_full, k & 1);
-      };
+      auto kv_ready = [&](uint32_t k) { return uwait(&ctl->kv_full[k & 1], (k >> 1) & 1); };
       auto q_ready = [&](uint32_t g) {
         const bool ok = uwait(&ctl->q_full[g % NQ], (g / NQ) & 1);
         ptx::tc_fence_after();
@@ -1105,7 +1106,8 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       auto issue_s_dp = [&](uint32_t g, uint32_t k, int h) {
         const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ + (g % NQ) * TB + h * (TB / 2)), 16);
         const uint32_t dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO + (g % NQ) * TB + h * (TB / 2)), 16);
-        const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK + (k & 1) * TB), 16);
+        const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB), 16);
+        const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB + TB), 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
           if (leader) ptx::mma_ss2(tA + h * 64, klo + ks * 2, kHi, qlo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
@@ -1121,7 +1123,6 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       if (ok) {
         issue_s_dp(0, 0, 0);
         issue_s_dp(0, 0, 1);
-        if (cur.n_steps == 1 && leader) ptx::mma_commit(&ctl->v_empty);
       }
       while (have && ok) {
         bool have_next = false;
@@ -1137,15 +1138,14 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
             // the first products of an item overwrite the accumulators: the item before has been read out
             if (h == 0 && n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
             ptx::tc_fence_after();
-            // dV and dK contract over the queries, 16 per k-step (2048 bytes of B); half h holds k-steps 4h .. 4h+3
+            // dV and dK contract over the queries, 16 per k-step (2048 bytes of B); half h holds k-steps
+            // 4h .. 4h+3, their P^T / dS^T in 8 columns at 16 (ks - 4h) of the half
 #pragma unroll
             for (int ks = 4 * h; ks < 4 * h + 4; ++ks)
-              if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
-                           (n > 0 || ks > 0) ? 1u : 0u);
+              if (leader) ptx::mma_ts2(tdV, tA + ks * 16, dolo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
             for (int ks = 4 * h; ks < 4 * h + 4; ++ks)
-              if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
-                           (n > 0 || ks > 0) ? 1u : 0u);
+              if (leader) ptx::mma_ts2(tdK, tB + ks * 16, qlo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
             if (h == 0) {
               if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
               next_step = ok && (!last || have_next);
@@ -1156,26 +1156,23 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
               // item's last step dV and dK are complete
               if (leader) ptx::mma_commit(&ctl->q_empty[st]);
               if (last && leader) ptx::mma_commit(&ctl->acc_full);
+              // dQ = dS K, contraction over the 128 keys: dS is the step's dS^T blocks read MN-major (the second
+              // half's block lies behind both buffers of the first half's)
+              if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
+              const uint32_t dslo_mn =
+                  ptx::smem_desc_lo(ptx::smem_u32(sdS + (g & 1) * C::kBlk), (2 - (g & 1)) * C::kBlk);
+              const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB), kHalfBytes);
+#pragma unroll
+              for (int ks = 0; ks < BM / 16; ++ks)
+                if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+              if (leader) ptx::mma_commit(&ctl->dq_full[g & 1]);
+              // every MMA of the item has been issued: its K / V stage goes back
+              if (last && leader) ptx::mma_commit(&ctl->kv_empty[k & 1]);
             }
-            // P^T / dS^T of this half have been consumed from TMEM (in issue order): the half's S^T / dP^T of
-            // the next step go in at once
+            // P^T / dS^T of this half have been consumed from TMEM (in issue order), and behind dQ the second
+            // half's dS^T block in shared memory: the half's S^T / dP^T of the next step go in at once
             if (next_step) issue_s_dp(g + 1, last ? k + 1 : k, h);
           }
-          if (!ok) break;
-          if (next_step) {
-            // V is free once dP^T of the last step of its item has been issued
-            const int n_of = last ? nxt.n_steps : cur.n_steps, idx = last ? 0 : n + 1;
-            if (idx + 1 == n_of && leader) ptx::mma_commit(&ctl->v_empty);
-          }
-          if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
-          const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (g & 1) * C::kDsBytes), kHalfBytes);
-          const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK + (k & 1) * TB), kHalfBytes);
-#pragma unroll
-          for (int ks = 0; ks < BM / 16; ++ks)  // contraction over the 128 keys
-            if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
-          if (leader) ptx::mma_commit(&ctl->dq_full[g & 1]);
-          // every MMA of the item has been issued: its K buffer goes back
-          if (last && leader) ptx::mma_commit(&ctl->k_empty[k & 1]);
         }
         cur = nxt;
         have = have_next;
@@ -1184,28 +1181,32 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
     }
   } else if (warp >= 16) {
     // ----------------------------------------------------------------- drain --
-    // dQ of every step (thread r = query row r; 32 columns at a time through the swizzled staging box and a TMA
-    // reduction: coalesced, rows beyond Lq are clipped by the tensor map), and dV / dK of the item (thread r =
-    // key row r, written directly) between the last two dQ.
+    // Warp j of this warpgroup owns TMEM lanes [32j, 32j+32): dQ of those query rows in every step (32 columns
+    // at a time through the warp's swizzled staging box and a TMA reduction: coalesced, rows beyond Lq are
+    // clipped by the tensor map), and dV / dK of those key rows (written directly) between the item's last two dQ.
     ptx::setmaxnreg_dec<48>();
-    const int r = tid & (BM - 1);
-    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int wj = warp & 3;
+    const int r = wj * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(wj * 32) << 16;
+    uint8_t* box = sdq + wj * C::kBox;
     bool ok = true;
+    // (the warp stays together: its waits' outcomes are made uniform)
+    auto wwait = [&](uint64_t* bar, uint32_t parity) {
+      if (ok) ok = __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
+    };
     ptx::grid_dep_wait();  // the reductions below need the dQ accumulator cleared by the pre-pass
     uint32_t g = 0;
     for (uint32_t k = 0;; ++k) {
       const int slot = k & 1;
-      if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
+      wwait(&ctl->item_full[slot], (k >> 1) & 1);
       const int w = ok ? ctl->item[slot] : -1;
       ptx::mbar_arrive(&ctl->item_empty[slot]);
-      // the warpgroup leaves as one (its named barriers count all 128 threads) when any of its waits ran out
-      if (ptx::named_barrier_or(1, BM, !ok)) break;
       if (w < 0) break;
       const Item it = decode_item(w);
       for (int n = 0; n < it.n_steps; ++n, ++g) {
         if (n + 1 == it.n_steps) {
           // dV, then dK: complete once the last step's products are (before its dQ)
-          if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
+          wwait(&ctl->acc_full, k & 1);
           ptx::tc_fence_after();
           const int kv_row = it.kv0 + r;
 #pragma unroll
@@ -1239,8 +1240,8 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
           }
         }
         const int h = it.hk * group + n / it.per_head;
-        const int q0 = (it.qt_begin + n % it.per_head) * BQ;
-        if (ok) ok = ptx::mbar_wait(&ctl->dq_full[g & 1], (g >> 1) & 1, abort_flag);
+        const int q0 = (it.qt_begin + n % it.per_head) * BQ + wj * 32;
+        wwait(&ctl->dq_full[g & 1], (g >> 1) & 1);
         ptx::tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
@@ -1251,27 +1252,26 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
             ptx::tc_fence_before();
             ptx::mbar_arrive(&ctl->dq_free[g & 1]);
           }
-          if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging box
-          ptx::named_barrier(1, BM);
+          if (lane == 0) ptx::bulk_wait_read();  // the previous reduction has read the box
+          __syncwarp();
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch)
-            *reinterpret_cast<uint4*>(sdq + r * 128 + ((ch ^ (r & 7)) << 4)) =
+            *reinterpret_cast<uint4*>(box + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
                 make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
           ptx::fence_proxy_async_smem();
-          ptx::named_barrier(1, BM);
-          if (r == 0 && ok) {
-            ptx::tma_reduce_add_4d(&tmdQ, sdq, cc * 32, q0, h, it.b);
+          __syncwarp();
+          if (lane == 0 && ok && q0 < a.Lq) {
+            ptx::tma_reduce_add_4d(&tmdQ, box, cc * 32, q0, h, it.b);
             ptx::bulk_commit();
           }
         }
       }
     }
-    if (r == 0) ptx::bulk_wait_all();
+    if (lane == 0) ptx::bulk_wait_all();
   } else {
     // --------------------------------------------------------------- compute --
     ptx::setmaxnreg_inc<96>();
-    const int wg = warp >> 2;      // which 32 queries of every step
-    const int half = wg >> 1;      // which half of the step
+    const int wg = warp >> 2;      // which 16 queries of each half of a step
     const int r = tid & (BM - 1);  // key row within the tile
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float c = a.scale * kLog2e;
@@ -1287,20 +1287,19 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       if (w < 0) break;
       const Item it = decode_item(w);
       const int kv_row = it.kv0 + r;
-      const bool row_valid = kv_row < it.kv_len;
       for (int n = 0; n < it.n_steps; ++n, ++g) {
         const int hq = it.hk * group + n / it.per_head;
         const int q0 = (it.qt_begin + n % it.per_head) * BQ;
         const float* vec = svec + (g & 1) * 2 * BQ;
-        uint8_t* ds_tile = sdS + (g & 1) * C::kDsBytes;
-        if (ok) ok = ptx::mbar_wait(&ctl->vec_full[g & 1], (g >> 1) & 1, abort_flag);
-        if (ok) ok = ptx::mbar_wait(&ctl->sp_full[half], g & 1, abort_flag);
-        ptx::tc_fence_after();
-        const bool diag = a.causal && q0 + it.shift < it.kv0 + BM;  // some (query, key) pairs of this step are masked
+        // some (query, key) pairs of this step are hidden: the diagonal step, a ragged last key tile
+        const bool diag = a.causal && q0 + it.shift < it.kv0 + BM;
         const bool masked = diag || it.kv0 + BM > it.kv_len;
+        if (ok) ok = ptx::mbar_wait(&ctl->vec_full[g & 1], (g >> 1) & 1, abort_flag);
 #pragma unroll
-        for (int sc = 0; sc < 2; ++sc) {
-          const int col = wg * 32 + sc * 16;  // 16 queries of the step
+        for (int h = 0; h < 2; ++h) {
+          const int col = h * 64 + wg * 16;  // this warpgroup's 16 queries of the half
+          if (ok) ok = ptx::mbar_wait(&ctl->sp_full[h], g & 1, abort_flag);
+          ptx::tc_fence_after();
           uint32_t s[16], dp[16];
           ptx::tmem_ld16(tA + lane_addr + col, s);
           ptx::tmem_ld16(tB + lane_addr + col, dp);
@@ -1309,26 +1308,27 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
           int64_t mo = 0;
           if constexpr (GEN)
             mo = it.b * a.mask.sb + hq * a.mask.sh + static_cast<int64_t>(q0 + col) * a.mask.sl + kv_row;
-          p_ds_chunk<BF16, GEN, T>(a, s, dp, vec + col, vec + BQ + col, c2v, sc2, masked, diag, row_valid, kv_row,
-                                   q0 + col, it.shift, mo, pk, dk);
-          // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the region, i.e. over the first 16
-          // columns it loaded itself, never over columns another warpgroup still has to read.
-          ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
-          ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
-          // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
-          uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
+          int n_hidden = 0;
+          if (masked) n_hidden = kv_row >= it.kv_len ? 16 : (diag ? kv_row - (q0 + col + it.shift) : 0);
+          p_ds_chunk<BF16, GEN, T>(a, s, dp, vec + col, vec + BQ + col, c2v, sc2, n_hidden, kv_row, q0 + col, mo, pk,
+                                   dk);
+          // (over the first 8 of the 16 columns just loaded, never over columns another warpgroup has to read)
+          ptx::tmem_st8(tA + lane_addr + col, pk);
+          ptx::tmem_st8(tB + lane_addr + col, dk);
+          // dS^T row r, the half's queries [16 wg, 16 wg + 16): two 16-byte chunks of the half's block
+          uint8_t* row = sdS + (h == 0 ? static_cast<int>(g & 1) : 2) * C::kBlk + r * 128;
 #pragma unroll
           for (int ch = 0; ch < 2; ++ch) {
-            const int chunk = ((col & 63) >> 3) + ch;
+            const int chunk = wg * 2 + ch;
             *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
                 make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
           }
+          if (h == 1) ptx::mbar_arrive(&ctl->vec_free[g & 1]);
+          ptx::tmem_wait_st();
+          ptx::fence_proxy_async_smem();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(&ctl->pds[h]);
         }
-        ptx::mbar_arrive(&ctl->vec_free[g & 1]);
-        ptx::tmem_wait_st();
-        ptx::fence_proxy_async_smem();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(&ctl->pds[half]);
       }
     }
   }
@@ -1370,7 +1370,7 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   if (!make_map(&tq, dtype, a.q, D, a.Lq, a.Hq, a.B, a.qs) || !make_map(&tk, dtype, a.k, D, a.Skv, a.Hkv, a.B, a.ks) ||
       !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs) ||
       !make_map(&tdo, dtype, a.d_o, D, a.Lq, a.Hq, a.B, a.dos) ||
-      !make_map_f32(&tdq, a.dq_accum, D, a.Lq, a.Hq, a.B))
+      !make_map_f32(&tdq, a.dq_accum, D, a.Lq, a.Hq, a.B, D == 64 ? 32 : 128))
     return cudaErrorInvalidValue;
   cudaError_t e;  // (dq_accum has been cleared by the delta pre-pass)
   void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, BwdArgs);

@@ -45,15 +45,15 @@ inline bool make_map(CUtensorMap* m, int dtype, const void* ptr, int D, int S, i
   return r == CUDA_SUCCESS;
 }
 
-// Dense fp32 [B, H, S, D] buffer, box = 32 floats (128 bytes) x 128 rows, for TMA reductions.
-inline bool make_map_f32(CUtensorMap* m, const float* ptr, int D, int S, int H, int B) {
+// Dense fp32 [B, H, S, D] buffer, box = 32 floats (128 bytes) x `box_rows` rows, for TMA reductions.
+inline bool make_map_f32(CUtensorMap* m, const float* ptr, int D, int S, int H, int B, int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
                         static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 4, static_cast<cuuint64_t>(S) * D * 4,
                            static_cast<cuuint64_t>(H) * S * D * 4};
-  cuuint32_t box[4] = {32, 128, 1, 1};
+  cuuint32_t box[4] = {32, static_cast<cuuint32_t>(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
