@@ -46,42 +46,31 @@ constexpr int kTmemCols = 512;
 constexpr int kHalfBytes = BM * 128;  // one 64-element column block of a 128-row tile
 
 struct __align__(8) SmemCtl {
-  uint64_t kv_full[2], kv_empty[2];    // K / V stages (work items alternate between them where two fit)
-  uint64_t acc_free;                   // dV / dK of the previous item have been read out of TMEM
-  uint64_t item_full[2], item_empty[2];
+  uint64_t item_full[2], item_empty[2];  // work items, from the producer to the issuer and the compute threads
   int item[2];
-  uint64_t q_full[2], q_empty[2];
-  uint64_t sp_full, pds_half, pds_full, acc_full;  // pds_half: the first 16 queries of every warpgroup are done
-  uint64_t dq_full[2], dq_free[2];  // per dQ buffer
-  uint64_t vec_full[2];             // per-query vectors of a step are in shared memory (written by warpgroup 0)
+  uint64_t kv_full, kv_empty;            // K / V of the current item
+  uint64_t q_full, q_empty;              // Q / dO of the current step
+  uint64_t vec_full[2];                  // per-query vectors of a step (buffer g & 1), written by the producer warp
+  uint64_t sp_full, pds_half, pds_full;  // pds_half: the first 16 queries of every warpgroup are done
+  uint64_t dq_full, dq_free;
+  uint64_t acc_full, acc_free;           // dV / dK of the item: complete / read out of TMEM
   uint32_t tmem_base;
   int abort_flag;
 };
 
-template <int D>
-struct Cfg {
-  static constexpr int TB = BM * D * 2;            // bytes of one tile
-  // With D = 64 there is room (TMEM columns and shared memory) to overlap the
-  // steps: two dQ accumulators, two dS^T tiles, two Q / dO stages, and dQ leaves
-  // through a staging tile and TMA reductions.  With D = 128 the steps run one
-  // after the other.
-  static constexpr bool kPipe = (D == 64);
-  static constexpr int NQ = kPipe ? 2 : 1;         // Q / dO ring depth
-  static constexpr int NKV = kPipe ? 2 : 1;        // K / V stages: the next work item's tiles load under this one's steps
-  // Warps: 16 compute (four warpgroups, 32 queries of every step each); D = 64: a warpgroup that drains results
-  // from TMEM; then the producer warp and the issuer warp (D = 64: in a warpgroup of their own, filled up with
-  // two idle warps, because register reallocation works on whole warpgroups).
-  static constexpr int kProdWarp = kPipe ? 20 : 16, kIssWarp = kProdWarp + 1;
-  static constexpr int kThreads = kPipe ? 768 : 576;
-  static constexpr int kItemConsumers = 1 + kCompute + (kPipe ? BM : 0);  // issuing lane, compute threads, drain
-  static constexpr int kDqReaders = kPipe ? BM : kCompute;  // threads that move a step's dQ out of TMEM
-  static constexpr int kAccReaders = kPipe ? BM : 2 * BM;   // threads that move dV / dK out
-  static constexpr int NDS = kPipe ? 2 : 1;        // dS^T tiles
-  static constexpr int kDsBytes = BM * BQ * 2;     // one dS^T tile
-  // dQ staging: boxes of 128 rows x 32 floats, D / 32 of them
-  static constexpr int kDqStage = (D / 32) * BQ * 128;
-  static constexpr int kVecBytes = 2 * 2 * BQ * 4; // lse / delta vectors per Q / dO stage
-  static constexpr int kSmem = 2 * NKV * TB + 2 * NQ * TB + NDS * kDsBytes + kDqStage + kVecBytes + 256;
+// D = 128 (the kernel below; D = 64 has its own further down).  TMEM has no columns left for a dQ accumulator
+// beside S^T, dP^T, dV and dK, so dQ reuses region A and the steps of an item run one after the other: one
+// Q / dO stage, one dS^T tile, one K / V stage.
+struct Cfg128 {
+  static constexpr int D = 128;
+  static constexpr int TB = BM * D * 2;  // bytes of one tile
+  // Warps: 16 compute (four warpgroups, 32 queries of every step each), then the producer warp and the issuer warp
+  static constexpr int kProdWarp = 16, kIssWarp = 17, kThreads = 576;
+  static constexpr int kItemConsumers = 1 + kCompute;  // issuing lane, compute threads
+  static constexpr int kDsBytes = BM * BQ * 2;         // the dS^T tile
+  static constexpr int kDqStage = (D / 32) * BQ * 128; // dQ staging: boxes of 128 rows x 32 floats, one per compute warpgroup
+  static constexpr int kVecBytes = 2 * 2 * BQ * 4;     // lse / delta vectors, two buffers
+  static constexpr int kSmem = 2 * TB + 2 * TB + kDsBytes + kDqStage + kVecBytes + 256;
   static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
 };
 
@@ -98,15 +87,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // GEN: the general variant (a mask and / or a causal triangle that is not top-left
 // aligned); the fast variant compiles all of that out.
-template <int D, bool BF16, bool GEN>
-__global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
+template <bool BF16, bool GEN>
+__global__ void __launch_bounds__(Cfg128::kThreads, 1)
     bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmdQ, const BwdArgs a) {
-  using C = Cfg<D>;
+  using C = Cfg128;
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-  constexpr int TB = C::TB, NQ = C::NQ, NKV = C::NKV, HALVES = D / 64;
-  constexpr bool kPipe = C::kPipe;
+  constexpr int D = C::D, TB = C::TB, HALVES = D / 64;
   // 128-byte-swizzled tiles must start on a 1024-byte boundary; with D = 128 there is
   // no room for alignment slack, so the array itself carries the requirement
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -114,12 +102,13 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
     if (threadIdx.x == 0 && a.status) atomicOr(a.status, kStatusBadSmemAlign);
     return;
   }
-  uint8_t* sKV = smem;               // NKV stages of [K tile | V tile]
-  uint8_t* sQ = sKV + NKV * 2 * TB;  // NQ tiles
-  uint8_t* sdO = sQ + NQ * TB;       // NQ tiles
-  uint8_t* sdS = sdO + NQ * TB;   // NDS x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
-  uint8_t* sdq = sdS + C::NDS * C::kDsBytes;  // dQ staging: boxes of [128 queries][32 floats], swizzled
-  float* svec = reinterpret_cast<float*>(sdq + C::kDqStage);  // [NQ stages][lse2 | delta][128]
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TB;
+  uint8_t* sQ = sV + TB;
+  uint8_t* sdO = sQ + TB;
+  uint8_t* sdS = sdO + TB;             // dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
+  uint8_t* sdq = sdS + C::kDsBytes;    // dQ staging: boxes of [128 queries][32 floats], swizzled
+  float* svec = reinterpret_cast<float*>(sdq + C::kDqStage);  // [2 buffers][lse2 | delta][128]
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(reinterpret_cast<uint8_t*>(svec) + C::kVecBytes);
   volatile int* abort_flag = &ctl->abort_flag;
 
@@ -168,17 +157,17 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
   if (warp == C::kProdWarp && lane == 0) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&ctl->kv_full[i], 1);
-      ptx::mbar_init(&ctl->kv_empty[i], 1);
       ptx::mbar_init(&ctl->item_full[i], 1);
       ptx::mbar_init(&ctl->item_empty[i], C::kItemConsumers);
-      ptx::mbar_init(&ctl->q_full[i], 1);
-      ptx::mbar_init(&ctl->q_empty[i], 1);
       ptx::mbar_init(&ctl->vec_full[i], 32);  // the lanes of the producer warp
-      ptx::mbar_init(&ctl->dq_full[i], 1);
-      ptx::mbar_init(&ctl->dq_free[i], C::kDqReaders);
     }
-    ptx::mbar_init(&ctl->acc_free, C::kAccReaders);
+    ptx::mbar_init(&ctl->kv_full, 1);
+    ptx::mbar_init(&ctl->kv_empty, 1);
+    ptx::mbar_init(&ctl->q_full, 1);
+    ptx::mbar_init(&ctl->q_empty, 1);
+    ptx::mbar_init(&ctl->dq_full, 1);
+    ptx::mbar_init(&ctl->dq_free, kCompute);
+    ptx::mbar_init(&ctl->acc_free, 2 * BM);  // the two warpgroups that read dV / dK out
     ptx::mbar_init(&ctl->sp_full, 1);
     ptx::mbar_init(&ctl->pds_full, kCompute);
     ptx::mbar_init(&ctl->pds_half, kCompute);
@@ -199,379 +188,240 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tA = tmem;              // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w) -> dQ (D = 128)
-  const uint32_t tB = tmem + 128;        // dP^T -> dS^T (16-bit pairs)
-  const uint32_t tdV = tmem + 256;       // D columns
-  const uint32_t tdK = tmem + 256 + D;   // D columns
-  // dQ of running step g: two buffers of D columns when there is room (D = 64), so that the
-  // read-out of one step overlaps the MMAs of the next; else region A is reused
-  auto tdQ = [&](uint32_t g) { return kPipe ? tmem + 384 + (g & 1) * D : tA; };
+  const uint32_t tA = tmem;             // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w) -> dQ
+  const uint32_t tB = tmem + 128;       // dP^T -> dS^T (16-bit pairs)
+  const uint32_t tdV = tmem + 256;      // D columns
+  const uint32_t tdK = tmem + 256 + D;  // D columns
 
   // Every role below walks the same sequence of items and, within an item, of steps; g counts the steps over
   // all items of this CTA (per-step barriers and buffers go by it), k the items (per-item barriers).
-  //
-  // dQ of step n of an item -> global: thread r owns query row q0 + r; 32-float column boxes go through
-  // swizzled staging tiles and TMA reductions (coalesced; rows beyond Lq are clipped by the tensor map).
-  // dV / dK: thread r owns key row kv0 + r and writes its D elements directly.
-  auto store_acc_row = [&](T* out, const uint32_t (&v)[32]) {
+  if (warp == C::kProdWarp) {
+    // -------------------------------------------------------------- producer --
+    // Lane 0 draws the items, publishes those with steps to the other warps and feeds their tiles by TMA; the
+    // whole warp fetches the per-query vectors of every step (-lse * log2(e) and -delta * scale).  A key tile
+    // that no query sees has no steps: the warp writes its zero gradients here and nobody else hears of it.
+    uint32_t gq = 0;  // steps of earlier items
+    bool dep_waited = false;
+    // per-query vectors of running step g into buffer g & 1
+    auto fetch_vec = [&](const Item& it, int n, uint32_t g) {
+      if (!dep_waited) {
+        // This kernel is launched early behind the delta pre-pass: barriers, TMEM and the first loads need
+        // only the inputs; delta is first read here.
+        ptx::grid_dep_wait();
+        dep_waited = true;
+      }
+      const int h = it.hk * group + n / it.per_head;
+      const int q0 = (it.qt_begin + n % it.per_head) * BQ;
+      float lv[4], dl[4];
+      const int64_t base = (static_cast<int64_t>(it.b) * a.Hq + h) * a.Lq + q0;
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
-      uint4 w4;
-      w4.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-      w4.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-      w4.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-      w4.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-      *reinterpret_cast<uint4*>(out + i) = w4;
-    }
-  };
-
-  if ((warp >> 2) == (C::kProdWarp >> 2)) {
-    // (D = 64: 96 registers for the 512 compute threads, 48 for the other 256: together the 80 x 768 the CTA
-    // was launched with, so the increase can always be served)
-    if constexpr (kPipe) ptx::setmaxnreg_dec<48>();
-    if (warp == C::kProdWarp) {
-      // ------------------------------------------------------------ producer --
-      // Lane 0 draws the items, publishes those with steps to the other warps and feeds their tiles by TMA; the
-      // whole warp fetches the per-query vectors of every step (-lse * log2(e) and -delta * scale) into the
-      // step's stage.  A key tile that no query sees has no steps: the warp writes its zero gradients here and
-      // nobody else hears of it (so a run of such items cannot fill the two-slot queue while the issuer looks
-      // one item ahead).
-      uint32_t gq = 0;  // steps requested in earlier items (ring position)
-      bool dep_waited = false;
-      // per-query vectors of running step g into buffer g & 1
-      auto fetch_vec = [&](const Item& it, int n, uint32_t g) {
-        if (!dep_waited) {
-          // This kernel is launched early behind the delta pre-pass: barriers, TMEM and the first loads need
-          // only the inputs; delta is first read here.
-          ptx::grid_dep_wait();
-          dep_waited = true;
+      for (int j = 0; j < 4; ++j) {
+        const int row = j * 32 + lane;
+        lv[j] = -INFINITY;  // rows beyond Lq behave like rows without any participating key: P = 0
+        dl[j] = 0.f;
+        if (q0 + row < a.Lq) {
+          lv[j] = a.lse[base + row];
+          dl[j] = a.delta[base + row];
         }
+      }
+      float* nv = svec + (g & 1) * 2 * BQ;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = j * 32 + lane;
+        nv[row] = lv[j] == -INFINITY ? -INFINITY : -lv[j] * kLog2e;
+        nv[BQ + row] = -dl[j] * a.scale;
+      }
+      ptx::mbar_arrive(&ctl->vec_full[g & 1]);
+    };
+    // The next item is drawn while the last step of this one is fed (lane 0 holds it in `drawn`), so that the
+    // latency of the atomic does not sit between two items.
+    int drawn = lane == 0 ? atomicAdd(a.sched, 1) : 0;
+    for (uint32_t i = 0;;) {  // i: items published so far
+      int w = drawn;
+      if (w >= n_items) w = -1;
+      w = __shfl_sync(0xffffffffu, w, 0);
+      const bool redraw = w >= 0;  // (nothing is drawn behind the end of the list)
+      Item it = {};
+      if (w >= 0) {
+        it = decode_item(w);
+        if (it.n_steps == 0) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            void* base = t == 0 ? a.dv : a.dk;
+            const Str3& st = t == 0 ? a.dvs : a.dks;
+            if (!base) continue;
+            T* out = reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h;
+            for (int e = lane; e < BM * (D / 8); e += 32) {
+              const int row = it.kv0 + e / (D / 8);
+              if (row < a.Skv)
+                *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * st.s + (e % (D / 8)) * 8) =
+                    make_uint4(0, 0, 0, 0);
+            }
+          }
+          if (lane == 0) drawn = atomicAdd(a.sched, 1);
+          continue;
+        }
+      }
+      int ok = 1;
+      if (lane == 0) {
+        const int slot = i & 1;
+        ok = ptx::mbar_wait(&ctl->item_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
+        if (ok) {
+          ctl->item[slot] = w;
+          ptx::mbar_arrive(&ctl->item_full[slot]);
+        }
+        // every MMA of the item before has completed
+        if (ok && w >= 0) ok = ptx::mbar_wait(&ctl->kv_empty, (i & 1) ^ 1, abort_flag);
+        if (ok && w >= 0) {
+          ptx::mbar_arrive_expect_tx(&ctl->kv_full, 2 * TB);
+#pragma unroll
+          for (int hf = 0; hf < HALVES; ++hf) {
+            ptx::tma_load_4d(sK + hf * kHalfBytes, &tmK, &ctl->kv_full, hf * 64, it.kv0, it.hk, it.b);
+            ptx::tma_load_4d(sV + hf * kHalfBytes, &tmV, &ctl->kv_full, hf * 64, it.kv0, it.hk, it.b);
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok || w < 0) break;
+      for (int n = 0; n < it.n_steps; ++n) {
+        if (redraw && n + 1 == it.n_steps && lane == 0) drawn = atomicAdd(a.sched, 1);
+        const uint32_t g = gq + n;
         const int h = it.hk * group + n / it.per_head;
         const int q0 = (it.qt_begin + n % it.per_head) * BQ;
-        float lv[4], dl[4];
-        const int64_t base = (static_cast<int64_t>(it.b) * a.Hq + h) * a.Lq + q0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int row = j * 32 + lane;
-          lv[j] = -INFINITY;  // rows beyond Lq behave like rows without any participating key: P = 0
-          dl[j] = 0.f;
-          if (q0 + row < a.Lq) {
-            lv[j] = a.lse[base + row];
-            dl[j] = a.delta[base + row];
-          }
-        }
-        float* nv = svec + (g & 1) * 2 * BQ;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int row = j * 32 + lane;
-          nv[row] = lv[j] == -INFINITY ? -INFINITY : -lv[j] * kLog2e;
-          nv[BQ + row] = -dl[j] * a.scale;
-        }
-        ptx::mbar_arrive(&ctl->vec_full[g & 1]);
-      };
-      for (uint32_t i = 0;;) {  // i: items published so far
-        int w = 0;
+        // The vectors (two buffers) are fetched a step ahead of the tiles (one stage): the wait passed for the
+        // tiles of step g - 1 says that step g - 2, the last to read this buffer, is over.
+        const bool vec_first = g > 0;
+        if (vec_first) fetch_vec(it, n, g);
         if (lane == 0) {
-          w = atomicAdd(a.sched, 1);
-          if (w >= n_items) w = -1;
-        }
-        w = __shfl_sync(0xffffffffu, w, 0);
-        Item it = {};
-        if (w >= 0) {
-          it = decode_item(w);
-          if (it.n_steps == 0) {
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              void* base = t == 0 ? a.dv : a.dk;
-              const Str3& st = t == 0 ? a.dvs : a.dks;
-              if (!base) continue;
-              T* out = reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h;
-              for (int e = lane; e < BM * (D / 8); e += 32) {
-                const int row = it.kv0 + e / (D / 8);
-                if (row < a.Skv)
-                  *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * st.s + (e % (D / 8)) * 8) =
-                      make_uint4(0, 0, 0, 0);
-              }
-            }
-            continue;
-          }
-        }
-        int ok = 1;
-        if (lane == 0) {
-          const int slot = i & 1;
-          ok = ptx::mbar_wait(&ctl->item_empty[slot], ((i >> 1) & 1) ^ 1, abort_flag);
+          // the MMAs that read Q / dO of the step before have completed
+          ok = ptx::mbar_wait(&ctl->q_empty, (g & 1) ^ 1, abort_flag);
           if (ok) {
-            ctl->item[slot] = w;
-            ptx::mbar_arrive(&ctl->item_full[slot]);
-          }
-          if (ok && w >= 0) {
-            // every MMA that read this stage (NKV items ago) has completed
-            const int ks = i % NKV;
-            uint8_t* sK = sKV + ks * 2 * TB;
-            uint8_t* sV = sK + TB;
-            ok = ptx::mbar_wait(&ctl->kv_empty[ks], ((i / NKV) & 1) ^ 1, abort_flag);
-            if (ok) {
-              ptx::mbar_arrive_expect_tx(&ctl->kv_full[ks], 2 * TB);
+            ptx::mbar_arrive_expect_tx(&ctl->q_full, 2 * TB);
 #pragma unroll
-              for (int hf = 0; hf < HALVES; ++hf) {
-                ptx::tma_load_4d(sK + hf * kHalfBytes, &tmK, &ctl->kv_full[ks], hf * 64, it.kv0, it.hk, it.b);
-                ptx::tma_load_4d(sV + hf * kHalfBytes, &tmV, &ctl->kv_full[ks], hf * 64, it.kv0, it.hk, it.b);
-              }
+            for (int hf = 0; hf < HALVES; ++hf) {
+              ptx::tma_load_4d(sQ + hf * kHalfBytes, &tmQ, &ctl->q_full, hf * 64, q0, h, it.b);
+              ptx::tma_load_4d(sdO + hf * kHalfBytes, &tmdO, &ctl->q_full, hf * 64, q0, h, it.b);
             }
           }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok || w < 0) break;
-        for (int n = 0; n < it.n_steps; ++n) {
-          const uint32_t g = gq + n;
-          const int st = g % NQ;
-          const int h = it.hk * group + n / it.per_head;
-          const int q0 = (it.qt_begin + n % it.per_head) * BQ;
-          // With a single Q / dO stage the vectors (two buffers) are fetched a step ahead of the tiles: the wait
-          // passed for the tiles of step g - 1 says that step g - 2, the last to read this buffer, is over.
-          const bool vec_first = NQ == 1 && g > 0;
-          if (vec_first) fetch_vec(it, n, g);
-          if (lane == 0) {
-            // the MMAs that read the stage's Q / dO have completed, and with them the element-wise phase that
-            // read its vectors
-            ok = ptx::mbar_wait(&ctl->q_empty[st], ((g / NQ) & 1) ^ 1, abort_flag);
-            if (ok) {
-              ptx::mbar_arrive_expect_tx(&ctl->q_full[st], 2 * TB);
+        if (!ok) break;
+        if (!vec_first) fetch_vec(it, n, g);
+      }
+      if (!ok) break;
+      gq += it.n_steps;
+      ++i;
+    }
+  } else if (warp == C::kIssWarp) {
+    // ---------------------------------------------------------------- issuer --
+    // The whole warp runs the loop (waits made uniform by a vote); one elected lane issues, so that addresses
+    // and descriptors stay warp-uniform.
+    const bool leader = ptx::elect_one();
+    auto uwait = [&](uint64_t* bar, uint32_t parity) {
+      return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
+    };
+    constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
+    const uint32_t fmt = BF16 ? 1 : 0;
+    const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ, fmt, 0, 0);   // S^T, dP^T: N = queries
+    const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);  // dV, dK: A from TMEM, B MN-major
+    const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);   // dQ: both operands MN-major
+    const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16), vlo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
+    const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sK), kHalfBytes);
+    const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16), dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO), 16);
+    const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ), kHalfBytes);
+    const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO), kHalfBytes);
+    const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS), kHalfBytes);
+    uint32_t fi = 0;  // items taken from the queue
+    // the next item, or false: none is left or a wait ran out
+    auto fetch = [&](Item& it) {
+      const int slot = fi & 1;
+      if (!uwait(&ctl->item_full[slot], (fi >> 1) & 1)) return false;
+      const int w = ctl->item[slot];
+      __syncwarp();  // every lane has read the slot
+      if (leader) ptx::mbar_arrive(&ctl->item_empty[slot]);
+      ++fi;
+      if (w < 0) return false;
+      it = decode_item(w);
+      return true;
+    };
+    // dP^T = V dO^T of running step g into region B
+    auto issue_dp = [&]() {
 #pragma unroll
-              for (int hf = 0; hf < HALVES; ++hf) {
-                ptx::tma_load_4d(sQ + st * TB + hf * kHalfBytes, &tmQ, &ctl->q_full[st], hf * 64, q0, h, it.b);
-                ptx::tma_load_4d(sdO + st * TB + hf * kHalfBytes, &tmdO, &ctl->q_full[st], hf * 64, q0, h, it.b);
-              }
-            }
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) break;
-          if (!vec_first) fetch_vec(it, n, g);
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+        if (leader) ptx::mma_ss2(tB, vlo + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+      }
+    };
+    // S^T = K Q^T into region A, and the step's first products are on their way
+    auto issue_s = [&]() {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+        if (leader) ptx::mma_ss2(tA, klo + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
+      }
+      if (leader) ptx::mma_commit(&ctl->sp_full);
+    };
+    Item cur = {}, nxt = {};
+    uint32_t g = 0, k = 0;
+    bool have = fetch(cur);
+    bool ok = have && uwait(&ctl->kv_full, 0) && uwait(&ctl->q_full, 0);
+    if (ok) {
+      ptx::tc_fence_after();
+      issue_dp();
+      issue_s();
+    }
+    while (have && ok) {
+      bool have_next = false;
+      for (int n = 0; n < cur.n_steps && ok; ++n, ++g) {
+        const bool last = n + 1 == cur.n_steps;
+        // dV and dK contract over the 128 queries, 16 per k-step (2048 bytes of B).  Warpgroup w forms
+        // the queries of k-step 2w first and of k-step 2w+1 second, so the even k-steps run while the
+        // odd ones are still being computed.
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (!(ok = uwait(half == 0 ? &ctl->pds_half : &ctl->pds_full, g & 1))) break;
+          // the first products of an item overwrite the accumulators: the item before has been read out
+          if (half == 0 && n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int ks = half; ks < BQ / 16; ks += 2)
+            if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+                         (n > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+          for (int ks = half; ks < BQ / 16; ks += 2)
+            if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+                         (n > 0 || ks > 0) ? 1u : 0u);
         }
         if (!ok) break;
-        gq += it.n_steps;
-        ++i;
-      }
-    } else if (warp == C::kIssWarp) {
-      // -------------------------------------------------------------- issuer --
-      // The whole warp runs the loop (waits made uniform by a vote); one elected lane issues, so that addresses
-      // and descriptors stay warp-uniform.
-      const bool leader = ptx::elect_one();
-      auto uwait = [&](uint64_t* bar, uint32_t parity) {
-        return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)) != 0;
-      };
-      constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
-      const uint32_t fmt = BF16 ? 1 : 0;
-      const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ, fmt, 0, 0);   // S^T, dP^T: N = queries
-      const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);  // dV, dK: A from TMEM, B MN-major
-      const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);   // dQ: both operands MN-major
-      auto klo = [&](uint32_t k) { return ptx::smem_desc_lo(ptx::smem_u32(sKV + (k % NKV) * 2 * TB), 16); };
-      auto vlo = [&](uint32_t k) { return ptx::smem_desc_lo(ptx::smem_u32(sKV + (k % NKV) * 2 * TB + TB), 16); };
-      auto klo_mn = [&](uint32_t k) {
-        return ptx::smem_desc_lo(ptx::smem_u32(sKV + (k % NKV) * 2 * TB), kHalfBytes);
-      };
-      auto stage_lo = [&](const uint8_t* base, uint32_t g, uint32_t lbo) {
-        return ptx::smem_desc_lo(ptx::smem_u32(base + (g % NQ) * TB), lbo);
-      };
-      uint32_t fi = 0;  // items taken from the queue
-      // the next item, or false: none is left or a wait ran out
-      auto fetch = [&](Item& it) {
-        const int slot = fi & 1;
-        if (!uwait(&ctl->item_full[slot], (fi >> 1) & 1)) return false;
-        const int w = ctl->item[slot];
-        __syncwarp();  // every lane has read the slot
-        if (leader) ptx::mbar_arrive(&ctl->item_empty[slot]);
-        ++fi;
-        if (w < 0) return false;
-        it = decode_item(w);
-        return true;
-      };
-      // K / V of the k-th item of this CTA are in shared memory
-      auto kv_ready = [&](uint32_t k) { return uwait(&ctl->kv_full[k % NKV], (k / NKV) & 1); };
-      // S^T = K Q^T and dP^T = V dO^T of running step g, on the tiles of the CTA's k-th item
-      auto issue_s_dp = [&](uint32_t g, uint32_t k) {
-        if (!uwait(&ctl->q_full[g % NQ], (g / NQ) & 1)) return false;
+        // Q and dO of this step have been read, and with these products the step's vectors: the stage is handed
+        // back here, so that its reload runs under the dQ MMAs and the read-out.  After the item's last step dV
+        // and dK are complete.
+        if (leader) ptx::mma_commit(&ctl->q_empty);
+        if (last && leader) ptx::mma_commit(&ctl->acc_full);
+#pragma unroll
+        for (int ks = 0; ks < BM / 16; ++ks)  // dQ = dS K into region A, contraction over the 128 keys
+          if (leader) ptx::mma_ss2(tA, dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+        if (leader) ptx::mma_commit(&ctl->dq_full);
+        // every MMA of the item has been issued: its K / V go back
+        if (last && leader) ptx::mma_commit(&ctl->kv_empty);
+        if (last) have_next = fetch(nxt) && (ok = uwait(&ctl->kv_full, (k + 1) & 1));
+        if (!ok || (last && !have_next)) break;
+        // dP^T of the next step can go into region B at once: dS^T there has been consumed in issue order.
+        // Region A holds this step's dQ until the compute threads have read it: S^T of the next step waits for that.
+        if (!(ok = uwait(&ctl->q_full, (g + 1) & 1))) break;
         ptx::tc_fence_after();
-        const uint32_t qlo = stage_lo(sQ, g, 16), dolo = stage_lo(sdO, g, 16), kl = klo(k), vl = vlo(k);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          if (leader) ptx::mma_ss2(tA, kl + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          if (leader) ptx::mma_ss2(tB, vl + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
-        }
-        if (leader) ptx::mma_commit(&ctl->sp_full);
-        return true;
-      };
-      Item cur = {}, nxt = {};
-      uint32_t g = 0, k = 0;
-      bool have = fetch(cur);
-      bool ok = have && kv_ready(0) && issue_s_dp(0, 0);
-      while (have && ok) {
-        bool have_next = false;
-        for (int n = 0; n < cur.n_steps && ok; ++n, ++g) {
-          const bool last = n + 1 == cur.n_steps;
-          const int st = g % NQ;
-          const uint32_t qlo_mn = stage_lo(sQ, g, kHalfBytes), dolo_mn = stage_lo(sdO, g, kHalfBytes);
-          const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (g % C::NDS) * C::kDsBytes), kHalfBytes);
-          // dV and dK contract over the 128 queries, 16 per k-step (2048 bytes of B).  Warpgroup w forms
-          // the queries of k-step 2w first and of k-step 2w+1 second, so the even k-steps run while the
-          // odd ones are still being computed.
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            if (!(ok = uwait(half == 0 ? &ctl->pds_half : &ctl->pds_full, g & 1))) break;
-            // the first products of an item overwrite the accumulators: the item before has been read out
-            if (half == 0 && n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
-            ptx::tc_fence_after();
-#pragma unroll
-            for (int ks = half; ks < BQ / 16; ks += 2)
-              if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
-                           (n > 0 || ks > 0) ? 1u : 0u);
-#pragma unroll
-            for (int ks = half; ks < BQ / 16; ks += 2)
-              if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
-                           (n > 0 || ks > 0) ? 1u : 0u);
-          }
-          if (!ok) break;
-          // Q and dO of this step have been read, and with these products the step's vectors; after the item's
-          // last step dV and dK are complete
-          if (leader) ptx::mma_commit(&ctl->q_empty[st]);
-          if (last && leader) ptx::mma_commit(&ctl->acc_full);
-          if (kPipe) {
-            // P^T / dS^T of this step have been consumed from TMEM (in issue order):
-            // the next step's S^T / dP^T go first (of the next item after this item's last step: its K / V
-            // sit in the other stage), then this step's dQ, which reads dS^T from shared memory
-            if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
-            if (!ok) break;
-            if ((!last || have_next) && !(ok = issue_s_dp(g + 1, last ? k + 1 : k))) break;
-            if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
-          }
-          const uint32_t kmn = klo_mn(k);
-#pragma unroll
-          for (int ks = 0; ks < BM / 16; ++ks) {  // contraction over the 128 keys
-            if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, kmn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
-          }
-          if (leader) ptx::mma_commit(&ctl->dq_full[kPipe ? (g & 1) : 0]);
-          // every MMA of the item has been issued: its K / V stage goes back
-          if (last && leader) ptx::mma_commit(&ctl->kv_empty[k % NKV]);
-          if (!kPipe) {
-            if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
-            if (!ok || (last && !have_next)) break;
-            const uint32_t kn = last ? k + 1 : k;
-            // (the single Q / dO stage was handed back after dK above, so its reload runs under
-            // the dQ MMAs and the read-out.)  dP^T of the next step can go into region B at once:
-            // dS^T there has been consumed in issue order.  Region A holds this step's dQ until the
-            // compute threads have read it: S^T of the next step waits for that.
-            if (!(ok = uwait(&ctl->q_full[(g + 1) % NQ], ((g + 1) / NQ) & 1))) break;
-            ptx::tc_fence_after();
-            const uint32_t qlo = stage_lo(sQ, g + 1, 16), dolo = stage_lo(sdO, g + 1, 16), kl = klo(kn), vl = vlo(kn);
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-              const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-              if (leader) ptx::mma_ss2(tB, vl + off, kHi, dolo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
-            }
-            if (!(ok = uwait(&ctl->dq_free[0], g & 1))) break;
-            ptx::tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-              const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-              if (leader) ptx::mma_ss2(tA, kl + off, kHi, qlo + off, kHi, idesc_s, ks > 0 ? 1u : 0u);
-            }
-            if (leader) ptx::mma_commit(&ctl->sp_full);
-          }
-        }
-        cur = nxt;
-        have = have_next;
-        ++k;
+        issue_dp();
+        if (!(ok = uwait(&ctl->dq_free, g & 1))) break;
+        ptx::tc_fence_after();
+        issue_s();
       }
-    }
-  } else if (kPipe && (warp >> 2) == 4) {
-    // ----------------------------------------------------------------- drain --
-    // D = 64: a warpgroup of its own moves the results out of TMEM, so that the compute warpgroups go from
-    // one step's element-wise phase straight into the next: dQ of every step (thread r = query row r, both
-    // 32-column boxes), and dV / dK of the item (thread r = key row r) between the last two dQ.
-    ptx::setmaxnreg_dec<48>();
-    if constexpr (kPipe) {
-      const int r = tid & (BM - 1);
-      const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      bool ok = true;
-      ptx::grid_dep_wait();  // the reductions below need the dQ accumulator cleared by the pre-pass
-      uint32_t g = 0;
-      for (uint32_t k = 0;; ++k) {
-        const int slot = k & 1;
-        if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
-        const int w = ok ? ctl->item[slot] : -1;
-        ptx::mbar_arrive(&ctl->item_empty[slot]);
-        // the warpgroup leaves as one (its named barriers count all 128 threads) when any of its waits ran out
-        if (ptx::named_barrier_or(1, BM, !ok)) break;
-        if (w < 0) break;
-        const Item it = decode_item(w);
-        for (int n = 0; n < it.n_steps; ++n, ++g) {
-          if (n + 1 == it.n_steps) {
-            // dV, then dK: complete once the last step's products are (before its dQ)
-            if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
-            ptx::tc_fence_after();
-            const int kv_row = it.kv0 + r;
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              void* base = t == 0 ? a.dv : a.dk;
-              const Str3& st = t == 0 ? a.dvs : a.dks;
-              T* out = base ? reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h + static_cast<int64_t>(kv_row) * st.s
-                            : nullptr;
-#pragma unroll
-              for (int cc = 0; cc < D / 32; ++cc) {
-                uint32_t v[32];
-                ptx::tmem_ld32((t == 0 ? tdV : tdK) + lane_addr + cc * 32, v);
-                ptx::tmem_wait_ld();
-                if (t == 1 && cc == D / 32 - 1) {
-                  // the accumulators may be overwritten by the next item's first products
-                  ptx::tc_fence_before();
-                  ptx::mbar_arrive(&ctl->acc_free);
-                }
-                if (ok && out && kv_row < a.Skv) store_acc_row(out + cc * 32, v);
-              }
-            }
-          }
-          const int h = it.hk * group + n / it.per_head;
-          const int q0 = (it.qt_begin + n % it.per_head) * BQ;
-          if (ok) ok = ptx::mbar_wait(&ctl->dq_full[g & 1], (g >> 1) & 1, abort_flag);
-          ptx::tc_fence_after();
-          if (r == 0) ptx::bulk_wait_read();  // the previous reductions have read the staging tiles
-          ptx::named_barrier(1, BM);
-#pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t v[32];
-            ptx::tmem_ld32(tdQ(g) + lane_addr + cc * 32, v);
-            ptx::tmem_wait_ld();
-            if (cc == D / 32 - 1) {
-              ptx::tc_fence_before();
-              ptx::mbar_arrive(&ctl->dq_free[g & 1]);
-            }
-            uint8_t* stage = sdq + cc * (BQ * 128);
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-              *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) =
-                  make_uint4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
-          }
-          ptx::fence_proxy_async_smem();
-          ptx::named_barrier(1, BM);
-          if (r == 0 && ok) {
-#pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc)
-              ptx::tma_reduce_add_4d(&tmdQ, sdq + cc * (BQ * 128), cc * 32, q0, h, it.b);
-            ptx::bulk_commit();
-          }
-        }
-      }
-      if (r == 0) ptx::bulk_wait_all();
+      cur = nxt;
+      have = have_next;
+      ++k;
     }
   } else {
     // --------------------------------------------------------------- compute --
-    if constexpr (kPipe) ptx::setmaxnreg_inc<96>();
-    const int wg = warp >> 2;   // which 32 queries of every step
+    const int wg = warp >> 2;      // which 32 queries of every step
     const int r = tid & (BM - 1);  // key row within the tile (phase 1) / query row of the step (dQ read-out)
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float c = a.scale * kLog2e;
@@ -587,10 +437,8 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
       if (ok) ok = ptx::mbar_wait(&ctl->item_full[slot], (k >> 1) & 1, abort_flag);
       const int w = ok ? ctl->item[slot] : -1;
       ptx::mbar_arrive(&ctl->item_empty[slot]);
-      if constexpr (!kPipe) {
-        // a warpgroup leaves as one (its named barriers below count all 128 threads) when any of its waits ran out
-        if (ptx::named_barrier_or(3 + wg, BM, !ok)) break;
-      }
+      // a warpgroup leaves as one (its named barriers below count all 128 threads) when any of its waits ran out
+      if (ptx::named_barrier_or(3 + wg, BM, !ok)) break;
       if (w < 0) break;
       const Item it = decode_item(w);
       const int b = it.b, hk = it.hk, kv0 = it.kv0, kv_len = it.kv_len, shift = it.shift, qt_begin = it.qt_begin,
@@ -598,19 +446,21 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
       const int kv_row = kv0 + r;
       const bool row_valid = kv_row < kv_len;
 
-      // D = 128: dQ of step n shares region A with S^T, so the four compute warpgroups move it out themselves
-      // (32 columns each) before the next step's S^T may be issued
+      // dQ of step n shares region A with S^T, so the four compute warpgroups move it out themselves before the
+      // next step's S^T may be issued: thread r owns query row q0 + r, warpgroup w the columns [32w, 32w+32),
+      // through a swizzled staging tile and one TMA reduction per warpgroup (coalesced; rows beyond Lq are
+      // clipped by the tensor map)
       auto read_out_dq = [&](int n) {
         const uint32_t g = g0 + n;
         const int h = hk * group + n / per_head;
         const int q0 = (qt_begin + n % per_head) * BQ;
-        if (ok) ok = ptx::mbar_wait(&ctl->dq_full[0], g & 1, abort_flag);
+        if (ok) ok = ptx::mbar_wait(&ctl->dq_full, g & 1, abort_flag);
         ptx::tc_fence_after();
         uint32_t v[32];
-        ptx::tmem_ld32(tdQ(g) + lane_addr + wg * 32, v);
+        ptx::tmem_ld32(tA + lane_addr + wg * 32, v);
         ptx::tmem_wait_ld();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(&ctl->dq_free[0]);
+        ptx::mbar_arrive(&ctl->dq_free);
         uint8_t* stage = sdq + wg * (BQ * 128);
         if (r == 0) ptx::bulk_wait_read();  // the previous reduction has read the staging tile
         ptx::named_barrier(3 + wg, BM);
@@ -631,7 +481,7 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
         const int q0 = (qt_begin + n % per_head) * BQ;
         // per-query vectors of the step, written by the producer warp: [0,128) -lse * log2(e), [128,256) -delta * scale
         const float* vec = svec + (g & 1) * 2 * BQ;
-        uint8_t* ds_tile = sdS + (g % C::NDS) * C::kDsBytes;
+        uint8_t* ds_tile = sdS;
         // all threads reach this point every step, expired waits included
         if (ok) ok = ptx::mbar_wait(&ctl->vec_full[g & 1], (g >> 1) & 1, abort_flag);
         if (ok) ok = ptx::mbar_wait(&ctl->sp_full, g & 1, abort_flag);
@@ -710,39 +560,45 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
         ptx::mbar_arrive(&ctl->pds_full);
-        if constexpr (!kPipe) read_out_dq(n);
+        read_out_dq(n);
       }
       g0 += n_steps;
 
-      if constexpr (!kPipe) {
-        // dV (warpgroup 0) and dK (warpgroup 1) of this key tile; the other warpgroups go on to the next item
-        if (wg < 2) {
-          T* out = nullptr;
-          if (wg == 0 && a.dv)
-            out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
-          if (wg == 1 && a.dk)
-            out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
-          if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
-          ptx::tc_fence_after();
-          const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
+      // dV (warpgroup 0) and dK (warpgroup 1) of this key tile; the other warpgroups go on to the next item
+      if (wg < 2) {
+        T* out = nullptr;
+        if (wg == 0 && a.dv)
+          out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
+        if (wg == 1 && a.dk)
+          out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
+        if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
+        ptx::tc_fence_after();
+        const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
 #pragma unroll 1
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t v[32];
-            ptx::tmem_ld32(src + cc * 32, v);
-            ptx::tmem_wait_ld();
-            if (cc == D / 32 - 1) {
-              // the accumulators may be overwritten by the next item's first products
-              ptx::tc_fence_before();
-              ptx::mbar_arrive(&ctl->acc_free);
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t v[32];
+          ptx::tmem_ld32(src + cc * 32, v);
+          ptx::tmem_wait_ld();
+          if (cc == D / 32 - 1) {
+            // the accumulators may be overwritten by the next item's first products
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&ctl->acc_free);
+          }
+          if (ok && out && kv_row < a.Skv) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w4;
+              w4.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+              w4.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              w4.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+              w4.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+              *reinterpret_cast<uint4*>(out + cc * 32 + i) = w4;
             }
-            if (ok && out && kv_row < a.Skv) store_acc_row(out + cc * 32, v);
           }
         }
       }
     }
-    if constexpr (!kPipe) {
-      if (r == 0) ptx::bulk_wait_all();
-    }
+    if (r == 0) ptx::bulk_wait_all();
   }
 
   ptx::tc_fence_before();
@@ -755,26 +611,25 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
 }
 
 // ------------------------------------------------------------------ D = 64 --
-// With 64 columns per head there is room to take the step apart in time.  The 128 queries of a step are two
-// halves of 64; S^T / dP^T of a half are MMAs with N = 64 into that half's columns of regions A and B.  All four
-// compute warpgroups work on one half at a time (16 queries each), then on the other, and the issuer alternates
-// likewise: when the first half's P^T / dS^T are ready it issues their dV / dK products and at once that half's
-// S^T / dP^T of the NEXT step; then the same for the second half, with the step's dQ in between.  So the
-// element-wise phase of one half runs while the tensor pipe works for the other, instead of the pipe and the
-// compute warps waiting for each other in turn.  A fifth warpgroup moves the results out of TMEM (each of its
-// warps the dQ of its 32 query rows through a staging box of its own and TMA reductions, and dV / dK of an
-// item between its last two dQ); the producer warp also fetches the per-query vectors.  Shared memory: two
-// K / V stages (the next item's first products are issued before this item's last dQ has read K), three Q / dO
-// stages (a stage is in use for two steps), dS^T as two blocks of 64 queries: two buffers for the first half
-// (the next step's is written while dQ reads this step's), one for the second (S^T / dP^T of the next step's
-// second half are issued behind dQ).
+// With 64 columns per head there is room (TMEM columns and shared memory) to take the step apart in time.  The
+// element-wise work of a step has two phases: P^T from S^T (the exponentials), then dS^T from dP^T and the P
+// kept in registers.  The issuer follows them: when P^T is ready it issues dV and at once S^T of the NEXT step
+// into region A; when dS^T is ready, dK, then dP^T of the next step into region B, then the step's dQ.  So each
+// phase of the compute warps runs while the tensor pipe works on what the other phase produced, instead of the
+// pipe and the compute warps waiting for each other in turn.  A fifth warpgroup moves the results out of TMEM
+// (each of its warps the dQ of its 32 query rows through a staging box of its own and TMA reductions, and dV /
+// dK of an item between its last two dQ); the producer warp also fetches the per-query vectors.  Shared memory:
+// two K / V stages (the next item's first products are issued before this item's last dQ has read K), three Q
+// stages (in use from S^T, a step ahead, to dK) and two dO stages (from dP^T to dV: half a step), two dS^T tiles.
 struct __align__(8) Ctl64 {
   uint64_t item_full[2], item_empty[2];
   uint64_t kv_full[2], kv_empty[2];
   uint64_t q_full[3], q_empty[3];
+  uint64_t do_full[2], do_empty[2];
   uint64_t vec_full[2];         // per-query vectors of a step (buffer g & 1), written by the producer warp
   uint64_t vec_free[2];         // ... and read by every compute thread
-  uint64_t sp_full[2], pds[2];  // per half: S^T / dP^T are in TMEM; P^T / dS^T have been formed
+  uint64_t s_full, dp_full;     // S^T / dP^T of a step are in TMEM
+  uint64_t p_done, ds_done;     // P^T / dS^T of a step have been formed
   uint64_t dq_full[2], dq_free[2];
   uint64_t acc_full, acc_free;
   int item[2];
@@ -784,26 +639,25 @@ struct __align__(8) Ctl64 {
 
 struct Cfg64 {
   static constexpr int D = 64, TB = BM * D * 2, NQ = 3;
-  static constexpr int kBlk = BM * 128;    // a dS^T block: 128 key rows x 64 queries
-  static constexpr int kBox = 32 * 128;    // a drain warp's staging box: 32 query rows x 32 floats
-  static constexpr int oKV = 0, oQ = 4 * TB, odO = oQ + NQ * TB, odS = odO + NQ * TB, oDq = odS + 3 * kBlk,
+  static constexpr int kDsBytes = BM * BQ * 2;  // a dS^T tile: [128 key rows][128 queries], two 64-query blocks
+  static constexpr int kBox = 32 * 128;         // a drain warp's staging box: 32 query rows x 32 floats
+  static constexpr int oKV = 0, oQ = 4 * TB, odO = oQ + NQ * TB, odS = odO + 2 * TB, oDq = odS + 2 * kDsBytes,
                        oVec = oDq + 4 * kBox, oCtl = oVec + 2 * 2 * BQ * 4;
-  static constexpr int kSmem = oCtl + 256;
-  static_assert(sizeof(Ctl64) <= 256, "control block");
+  static constexpr int kSmem = oCtl + 512;
+  static_assert(sizeof(Ctl64) <= 512, "control block");
   static_assert(kSmem <= 232448, "exceeds the shared memory a CTA may request");
   // warps: 16 compute, 4 drain, producer, issuer, 2 idle (register reallocation works on whole warpgroups)
   static constexpr int kProdWarp = 20, kIssWarp = 21, kThreads = 768;
 };
 
-// P^T and dS^T of 16 queries for this thread's key row, as packed 16-bit pairs.  s / dp: S^T and dP^T (fp32
-// bits); lse2 / dsc: -lse * log2(e) and -delta * scale of the 16 queries; q_first: index of the first query;
-// mo: offset of (first query, this key) in the mask; n_hidden: how many of the 16 queries, from the first on,
-// do not see this key (causal triangle; all 16 for a key beyond kv_len).
+// P of 16 queries for this thread's key row: in place of s (S^T, fp32 bits) and as packed 16-bit pairs in pk.
+// lse2: -lse * log2(e) of the 16 queries; q_first: index of the first query; mo: offset of (first query, this
+// key) in the mask; n_hidden: how many of the 16 queries, from the first on, do not see this key (causal
+// triangle; all 16 for a key beyond kv_len).
 template <bool BF16, bool GEN, typename T>
-__device__ __forceinline__ void p_ds_chunk(const BwdArgs& a, uint32_t (&s)[16], const uint32_t (&dp)[16],
-                                           const float* lse2, const float* dsc, float2 c2v, float2 sc2, int n_hidden,
-                                           int kv_row, int q_first, int64_t mo, uint32_t (&pk)[8], uint32_t (&dk)[8]) {
-  // exponents c*s - lse2, in packed fp32 pairs, in place
+__device__ __forceinline__ void p_chunk(const BwdArgs& a, uint32_t (&s)[16], const float* lse2, float2 c2v,
+                                        int n_hidden, int kv_row, int q_first, int64_t mo, uint32_t (&pk)[8]) {
+  // exponents c*s - lse2, in packed fp32 pairs
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
     const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i);
@@ -833,19 +687,31 @@ __device__ __forceinline__ void p_ds_chunk(const BwdArgs& a, uint32_t (&s)[16], 
   }
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
-    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
-    // P = 2^x, dS = P * (scale*dP - scale*delta)
     // (one exponential in eight on the FMA pipe: the compute warps saturate the MUFU units in this phase)
-    const float2 p0 = make_float2(ptx::ex2(__uint_as_float(s[i])), ptx::ex2(__uint_as_float(s[i + 1])));
-    const float2 p1 = make_float2(ptx::ex2(__uint_as_float(s[i + 2])),
-                                  (i & 4) ? ptx::ex2_fma(__uint_as_float(s[i + 3])) : ptx::ex2(__uint_as_float(s[i + 3])));
+    const float p0 = ptx::ex2(__uint_as_float(s[i])), p1 = ptx::ex2(__uint_as_float(s[i + 1]));
+    const float p2 = ptx::ex2(__uint_as_float(s[i + 2]));
+    const float p3 = (i & 4) ? ptx::ex2_fma(__uint_as_float(s[i + 3])) : ptx::ex2(__uint_as_float(s[i + 3]));
+    s[i] = __float_as_uint(p0), s[i + 1] = __float_as_uint(p1);
+    s[i + 2] = __float_as_uint(p2), s[i + 3] = __float_as_uint(p3);
+    pk[(i >> 1) + 0] = pack2<BF16>(p0, p1);
+    pk[(i >> 1) + 1] = pack2<BF16>(p2, p3);
+  }
+}
+
+// dS = P * (scale * dP - scale * delta) of 16 queries, as packed 16-bit pairs.  p: P (fp32 bits); dp: dP^T
+// (fp32 bits); dsc: -delta * scale of the 16 queries.
+template <bool BF16>
+__device__ __forceinline__ void ds_chunk(const uint32_t (&p)[16], const uint32_t (&dp)[16], const float* dsc,
+                                         float2 sc2, uint32_t (&dk)[8]) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
     const float2 g0 =
         ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2, make_float2(d4.x, d4.y));
     const float2 g1 =
         ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2, make_float2(d4.z, d4.w));
-    const float2 ds0 = ptx::mul2(p0, g0), ds1 = ptx::mul2(p1, g1);
-    pk[(i >> 1) + 0] = pack2<BF16>(p0.x, p0.y);
-    pk[(i >> 1) + 1] = pack2<BF16>(p1.x, p1.y);
+    const float2 ds0 = ptx::mul2(make_float2(__uint_as_float(p[i]), __uint_as_float(p[i + 1])), g0);
+    const float2 ds1 = ptx::mul2(make_float2(__uint_as_float(p[i + 2]), __uint_as_float(p[i + 3])), g1);
     dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
     dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
   }
@@ -866,10 +732,8 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
   }
   uint8_t* sKV = smem + C::oKV;  // 2 stages of [K tile | V tile]
   uint8_t* sQ = smem + C::oQ;    // NQ stages
-  uint8_t* sdO = smem + C::odO;  // NQ stages
-  // dS^T, [128 key rows][64 queries] blocks with 128-byte swizzle: first half of step g in block g & 1, second
-  // half in block 2
-  uint8_t* sdS = smem + C::odS;
+  uint8_t* sdO = smem + C::odO;  // 2 stages
+  uint8_t* sdS = smem + C::odS;  // 2 x dS^T: [128 key rows][128 queries], two 64-query blocks, 128-byte swizzle
   uint8_t* sdq = smem + C::oDq;  // dQ staging: per drain warp [32 queries][32 floats], swizzled
   float* svec = reinterpret_cast<float*>(smem + C::oVec);  // [2 buffers][lse2 | delta][128]
   Ctl64* ctl = reinterpret_cast<Ctl64*>(smem + C::oCtl);
@@ -924,8 +788,8 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       ptx::mbar_init(&ctl->kv_empty[i], 1);
       ptx::mbar_init(&ctl->vec_full[i], 32);  // the lanes of the producer warp
       ptx::mbar_init(&ctl->vec_free[i], kCompute);
-      ptx::mbar_init(&ctl->sp_full[i], 1);
-      ptx::mbar_init(&ctl->pds[i], kCompute);
+      ptx::mbar_init(&ctl->do_full[i], 1);
+      ptx::mbar_init(&ctl->do_empty[i], 1);
       ptx::mbar_init(&ctl->dq_full[i], 1);
       ptx::mbar_init(&ctl->dq_free[i], BM);
     }
@@ -934,6 +798,10 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       ptx::mbar_init(&ctl->q_full[i], 1);
       ptx::mbar_init(&ctl->q_empty[i], 1);
     }
+    ptx::mbar_init(&ctl->s_full, 1);
+    ptx::mbar_init(&ctl->dp_full, 1);
+    ptx::mbar_init(&ctl->p_done, kCompute);
+    ptx::mbar_init(&ctl->ds_done, kCompute);
     ptx::mbar_init(&ctl->acc_full, 1);
     ptx::mbar_init(&ctl->acc_free, BM);
     ctl->abort_flag = 0;
@@ -952,10 +820,8 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-  // Regions A (S^T -> P^T) and B (dP^T -> dS^T): half h in columns [64h, 64h+64), warpgroup w's 16 queries of
-  // the half in [64h + 16w, +16); their 16-bit results go over the first 8 of those columns.
-  const uint32_t tA = tmem;
-  const uint32_t tB = tmem + 128;
+  const uint32_t tA = tmem;         // S^T -> P^T (16-bit pairs in cols [32w, 32w+16) per warpgroup w)
+  const uint32_t tB = tmem + 128;   // dP^T -> dS^T, likewise
   const uint32_t tdV = tmem + 256;  // 64 columns
   const uint32_t tdK = tmem + 320;  // 64 columns
   auto tdQ = [&](uint32_t g) { return tmem + 384 + (g & 1) * D; };  // dQ of running step g
@@ -974,13 +840,14 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       // (so a run of such items cannot fill the two-slot queue while the issuer looks one item ahead).
       uint32_t gq = 0;  // steps of earlier items
       bool dep_waited = false;
+      // The next item is drawn while the last step of this one is fed (lane 0 holds it in `drawn`), so that the
+      // latency of the atomic does not sit between two items.
+      int drawn = lane == 0 ? atomicAdd(a.sched, 1) : 0;
       for (uint32_t i = 0;;) {  // i: items published so far
-        int w = 0;
-        if (lane == 0) {
-          w = atomicAdd(a.sched, 1);
-          if (w >= n_items) w = -1;
-        }
+        int w = drawn;
+        if (w >= n_items) w = -1;
         w = __shfl_sync(0xffffffffu, w, 0);
+        bool redraw = w >= 0;  // (nothing is drawn behind the end of the list)
         Item it = {};
         if (w >= 0) {
           it = decode_item(w);
@@ -998,6 +865,7 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
                       make_uint4(0, 0, 0, 0);
               }
             }
+            if (lane == 0) drawn = atomicAdd(a.sched, 1);
             continue;
           }
         }
@@ -1020,6 +888,7 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok || w < 0) break;
         for (int n = 0; n < it.n_steps; ++n) {
+          if (redraw && n + 1 == it.n_steps && lane == 0) drawn = atomicAdd(a.sched, 1);
           const uint32_t g = gq + n;
           const int st = g % NQ;
           const int h = it.hk * group + n / it.per_head;
@@ -1027,9 +896,13 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
           if (lane == 0) {
             ok = ptx::mbar_wait(&ctl->q_empty[st], ((g / NQ) & 1) ^ 1, abort_flag);
             if (ok) {
-              ptx::mbar_arrive_expect_tx(&ctl->q_full[st], 2 * TB);
+              ptx::mbar_arrive_expect_tx(&ctl->q_full[st], TB);
               ptx::tma_load_4d(sQ + st * TB, &tmQ, &ctl->q_full[st], 0, q0, h, it.b);
-              ptx::tma_load_4d(sdO + st * TB, &tmdO, &ctl->q_full[st], 0, q0, h, it.b);
+              ok = ptx::mbar_wait(&ctl->do_empty[g & 1], ((g >> 1) & 1) ^ 1, abort_flag);
+            }
+            if (ok) {
+              ptx::mbar_arrive_expect_tx(&ctl->do_full[g & 1], TB);
+              ptx::tma_load_4d(sdO + (g & 1) * TB, &tmdO, &ctl->do_full[g & 1], 0, q0, h, it.b);
             }
             // The vectors' buffer was last read in step g - 2.  (A barrier per buffer: it cannot complete its next
             // phase before this warp has written the buffer again, so the parity below is never ambiguous, as it
@@ -1079,9 +952,9 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       };
       constexpr uint32_t kHi = ptx::smem_desc_hi_sw128(1024);
       const uint32_t fmt = BF16 ? 1 : 0;
-      const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ / 2, fmt, 0, 0);  // S^T, dP^T of a half: N = 64 queries
-      const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);     // dV, dK: A from TMEM, B MN-major
-      const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);      // dQ: both operands MN-major
+      const uint32_t idesc_s = ptx::make_idesc_f16(BM, BQ, fmt, 0, 0);   // S^T, dP^T: N = queries
+      const uint32_t idesc_acc = ptx::make_idesc_f16(BM, D, fmt, 0, 1);  // dV, dK: A from TMEM, B MN-major
+      const uint32_t idesc_dq = ptx::make_idesc_f16(BQ, D, fmt, 1, 1);   // dQ: both operands MN-major
       uint32_t fi = 0;  // items taken from the queue
       // the next item, or false: none is left or a wait ran out
       auto fetch = [&](Item& it) {
@@ -1097,82 +970,76 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       };
       // K and V of the k-th item of this CTA are in shared memory
       auto kv_ready = [&](uint32_t k) { return uwait(&ctl->kv_full[k & 1], (k >> 1) & 1); };
-      auto q_ready = [&](uint32_t g) {
-        const bool ok = uwait(&ctl->q_full[g % NQ], (g / NQ) & 1);
+      // S^T = K Q^T of running step g, on the tiles of the CTA's k-th item
+      auto issue_s = [&](uint32_t g, uint32_t k) {
+        if (!uwait(&ctl->q_full[g % NQ], (g / NQ) & 1)) return false;
         ptx::tc_fence_after();
-        return ok;
-      };
-      // S^T = K Q^T and dP^T = V dO^T of half h of running step g, on the tiles of the CTA's k-th item
-      auto issue_s_dp = [&](uint32_t g, uint32_t k, int h) {
-        const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ + (g % NQ) * TB + h * (TB / 2)), 16);
-        const uint32_t dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO + (g % NQ) * TB + h * (TB / 2)), 16);
+        const uint32_t qlo = ptx::smem_desc_lo(ptx::smem_u32(sQ + (g % NQ) * TB), 16);
         const uint32_t klo = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB), 16);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          if (leader) ptx::mma_ss2(tA, klo + ks * 2, kHi, qlo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
+        if (leader) ptx::mma_commit(&ctl->s_full);
+        return true;
+      };
+      // dP^T = V dO^T of running step g
+      auto issue_dp = [&](uint32_t g, uint32_t k) {
+        if (!uwait(&ctl->do_full[g & 1], (g >> 1) & 1)) return false;
+        ptx::tc_fence_after();
+        const uint32_t dolo = ptx::smem_desc_lo(ptx::smem_u32(sdO + (g & 1) * TB), 16);
         const uint32_t vlo = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB + TB), 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
-          if (leader) ptx::mma_ss2(tA + h * 64, klo + ks * 2, kHi, qlo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          if (leader) ptx::mma_ss2(tB + h * 64, vlo + ks * 2, kHi, dolo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
-        if (leader) ptx::mma_commit(&ctl->sp_full[h]);
+          if (leader) ptx::mma_ss2(tB, vlo + ks * 2, kHi, dolo + ks * 2, kHi, idesc_s, ks > 0 ? 1u : 0u);
+        if (leader) ptx::mma_commit(&ctl->dp_full);
+        return true;
       };
       Item cur = {}, nxt = {};
       uint32_t g = 0, k = 0;
       bool have = fetch(cur);
-      bool ok = have && kv_ready(0) && q_ready(0);
-      if (ok) {
-        issue_s_dp(0, 0, 0);
-        issue_s_dp(0, 0, 1);
-      }
+      bool ok = have && kv_ready(0) && issue_s(0, 0) && issue_dp(0, 0);
       while (have && ok) {
         bool have_next = false;
         for (int n = 0; n < cur.n_steps && ok; ++n, ++g) {
           const bool last = n + 1 == cur.n_steps;
-          const int st = g % NQ;
-          const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ + st * TB), kHalfBytes);
-          const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO + st * TB), kHalfBytes);
-          bool next_step = false;  // there is a step g + 1 (of this item or the next)
+          const uint32_t qlo_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ + (g % NQ) * TB), kHalfBytes);
+          const uint32_t dolo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdO + (g & 1) * TB), kHalfBytes);
+          // P^T is ready: dV += P^T dO, contraction over the queries, 16 per k-step (2048 bytes of B)
+          if (!(ok = uwait(&ctl->p_done, g & 1))) break;
+          // the first products of an item overwrite the accumulators: the item before has been read out
+          if (n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
+          ptx::tc_fence_after();
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (!(ok = uwait(&ctl->pds[h], g & 1))) break;
-            // the first products of an item overwrite the accumulators: the item before has been read out
-            if (h == 0 && n == 0 && !(ok = uwait(&ctl->acc_free, (k & 1) ^ 1))) break;
-            ptx::tc_fence_after();
-            // dV and dK contract over the queries, 16 per k-step (2048 bytes of B); half h holds k-steps
-            // 4h .. 4h+3, their P^T / dS^T in 8 columns at 16 (ks - 4h) of the half
+          for (int ks = 0; ks < BQ / 16; ++ks)
+            if (leader) ptx::mma_ts2(tdV, tA + (ks >> 1) * 32 + (ks & 1) * 8, dolo_mn + ks * 128, kHi, idesc_acc,
+                         (n > 0 || ks > 0) ? 1u : 0u);
+          if (leader) ptx::mma_commit(&ctl->do_empty[g & 1]);  // dO of this step has been read (dP^T before, dV now)
+          // P^T has been consumed from region A (in issue order): S^T of the next step goes in at once (of the
+          // next item after this item's last step: its K / V sit in the other stage)
+          if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
+          const bool next_step = ok && (!last || have_next);
+          const uint32_t kn = last ? k + 1 : k;
+          if (!ok || (next_step && !(ok = issue_s(g + 1, kn)))) break;
+          // dS^T is ready: dK += dS^T Q; then dP^T of the next step into region B; then dQ = dS K (contraction
+          // over the 128 keys; dS is the step's dS^T tile in shared memory read MN-major)
+          if (!(ok = uwait(&ctl->ds_done, g & 1))) break;
+          ptx::tc_fence_after();
 #pragma unroll
-            for (int ks = 4 * h; ks < 4 * h + 4; ++ks)
-              if (leader) ptx::mma_ts2(tdV, tA + ks * 16, dolo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < BQ / 16; ++ks)
+            if (leader) ptx::mma_ts2(tdK, tB + (ks >> 1) * 32 + (ks & 1) * 8, qlo_mn + ks * 128, kHi, idesc_acc,
+                         (n > 0 || ks > 0) ? 1u : 0u);
+          if (leader) ptx::mma_commit(&ctl->q_empty[g % NQ]);  // Q of this step has been read (S^T before, dK now)
+          if (last && leader) ptx::mma_commit(&ctl->acc_full);  // dV and dK of the item are complete
+          if (next_step && !(ok = issue_dp(g + 1, kn))) break;
+          if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
+          const uint32_t dslo_mn = ptx::smem_desc_lo(ptx::smem_u32(sdS + (g & 1) * C::kDsBytes), kHalfBytes);
+          const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB), kHalfBytes);
 #pragma unroll
-            for (int ks = 4 * h; ks < 4 * h + 4; ++ks)
-              if (leader) ptx::mma_ts2(tdK, tB + ks * 16, qlo_mn + ks * 128, kHi, idesc_acc, (n > 0 || ks > 0) ? 1u : 0u);
-            if (h == 0) {
-              if (last) have_next = fetch(nxt) && (ok = kv_ready(k + 1));
-              next_step = ok && (!last || have_next);
-              if (next_step) ok = q_ready(g + 1);
-              if (!ok) break;
-            } else {
-              // Q and dO of this step have been read, and with these products the step's vectors; after the
-              // item's last step dV and dK are complete
-              if (leader) ptx::mma_commit(&ctl->q_empty[st]);
-              if (last && leader) ptx::mma_commit(&ctl->acc_full);
-              // dQ = dS K, contraction over the 128 keys: dS is the step's dS^T blocks read MN-major (the second
-              // half's block lies behind both buffers of the first half's)
-              if (g >= 2 && !(ok = uwait(&ctl->dq_free[g & 1], ((g >> 1) - 1) & 1))) break;
-              const uint32_t dslo_mn =
-                  ptx::smem_desc_lo(ptx::smem_u32(sdS + (g & 1) * C::kBlk), (2 - (g & 1)) * C::kBlk);
-              const uint32_t klo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV + (k & 1) * 2 * TB), kHalfBytes);
-#pragma unroll
-              for (int ks = 0; ks < BM / 16; ++ks)
-                if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
-              if (leader) ptx::mma_commit(&ctl->dq_full[g & 1]);
-              // every MMA of the item has been issued: its K / V stage goes back
-              if (last && leader) ptx::mma_commit(&ctl->kv_empty[k & 1]);
-            }
-            // P^T / dS^T of this half have been consumed from TMEM (in issue order), and behind dQ the second
-            // half's dS^T block in shared memory: the half's S^T / dP^T of the next step go in at once
-            if (next_step) issue_s_dp(g + 1, last ? k + 1 : k, h);
-          }
+          for (int ks = 0; ks < BM / 16; ++ks)
+            if (leader) ptx::mma_ss2(tdQ(g), dslo_mn + ks * 128, kHi, klo_mn + ks * 128, kHi, idesc_dq, ks > 0 ? 1u : 0u);
+          if (leader) ptx::mma_commit(&ctl->dq_full[g & 1]);
+          // every MMA of the item has been issued: its K / V stage goes back
+          if (last && leader) ptx::mma_commit(&ctl->kv_empty[k & 1]);
         }
         cur = nxt;
         have = have_next;
@@ -1271,7 +1138,7 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
   } else {
     // --------------------------------------------------------------- compute --
     ptx::setmaxnreg_inc<96>();
-    const int wg = warp >> 2;      // which 16 queries of each half of a step
+    const int wg = warp >> 2;      // which 32 queries of every step
     const int r = tid & (BM - 1);  // key row within the tile
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float c = a.scale * kLog2e;
@@ -1295,40 +1162,55 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
         const bool diag = a.causal && q0 + it.shift < it.kv0 + BM;
         const bool masked = diag || it.kv0 + BM > it.kv_len;
         if (ok) ok = ptx::mbar_wait(&ctl->vec_full[g & 1], (g >> 1) & 1, abort_flag);
+        // phase 1: P^T from S^T; P stays in registers for phase 2
+        if (ok) ok = ptx::mbar_wait(&ctl->s_full, g & 1, abort_flag);
+        ptx::tc_fence_after();
+        uint32_t p[2][16];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int col = h * 64 + wg * 16;  // this warpgroup's 16 queries of the half
-          if (ok) ok = ptx::mbar_wait(&ctl->sp_full[h], g & 1, abort_flag);
-          ptx::tc_fence_after();
-          uint32_t s[16], dp[16];
-          ptx::tmem_ld16(tA + lane_addr + col, s);
-          ptx::tmem_ld16(tB + lane_addr + col, dp);
+        for (int sc = 0; sc < 2; ++sc) {
+          const int col = wg * 32 + sc * 16;  // 16 queries of the step
+          ptx::tmem_ld16(tA + lane_addr + col, p[sc]);
           ptx::tmem_wait_ld();
-          uint32_t pk[8], dk[8];
+          uint32_t pk[8];
           int64_t mo = 0;
           if constexpr (GEN)
             mo = it.b * a.mask.sb + hq * a.mask.sh + static_cast<int64_t>(q0 + col) * a.mask.sl + kv_row;
           int n_hidden = 0;
           if (masked) n_hidden = kv_row >= it.kv_len ? 16 : (diag ? kv_row - (q0 + col + it.shift) : 0);
-          p_ds_chunk<BF16, GEN, T>(a, s, dp, vec + col, vec + BQ + col, c2v, sc2, n_hidden, kv_row, q0 + col, mo, pk,
-                                   dk);
-          // (over the first 8 of the 16 columns just loaded, never over columns another warpgroup has to read)
-          ptx::tmem_st8(tA + lane_addr + col, pk);
-          ptx::tmem_st8(tB + lane_addr + col, dk);
-          // dS^T row r, the half's queries [16 wg, 16 wg + 16): two 16-byte chunks of the half's block
-          uint8_t* row = sdS + (h == 0 ? static_cast<int>(g & 1) : 2) * C::kBlk + r * 128;
+          p_chunk<BF16, GEN, T>(a, p[sc], vec + col, c2v, n_hidden, kv_row, q0 + col, mo, pk);
+          // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the region, i.e. over the first 16
+          // columns it loaded itself, never over columns another warpgroup still has to read.
+          ptx::tmem_st8(tA + lane_addr + wg * 32 + sc * 8, pk);
+        }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->p_done);
+        // phase 2: dS^T from dP^T and P, to TMEM (for dK) and to shared memory (for dQ)
+        uint8_t* ds_tile = sdS + (g & 1) * C::kDsBytes;
+        if (ok) ok = ptx::mbar_wait(&ctl->dp_full, g & 1, abort_flag);
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int sc = 0; sc < 2; ++sc) {
+          const int col = wg * 32 + sc * 16;
+          uint32_t dp[16], dk[8];
+          ptx::tmem_ld16(tB + lane_addr + col, dp);
+          ptx::tmem_wait_ld();
+          ds_chunk<BF16>(p[sc], dp, vec + BQ + col, sc2, dk);
+          ptx::tmem_st8(tB + lane_addr + wg * 32 + sc * 8, dk);
+          // dS^T row r, queries [col, col+16): two 16-byte chunks of the 64-query block col/64
+          uint8_t* row = ds_tile + (col >> 6) * kHalfBytes + r * 128;
 #pragma unroll
           for (int ch = 0; ch < 2; ++ch) {
-            const int chunk = wg * 2 + ch;
+            const int chunk = ((col & 63) >> 3) + ch;
             *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
                 make_uint4(dk[ch * 4 + 0], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
           }
-          if (h == 1) ptx::mbar_arrive(&ctl->vec_free[g & 1]);
-          ptx::tmem_wait_st();
-          ptx::fence_proxy_async_smem();
-          ptx::tc_fence_before();
-          ptx::mbar_arrive(&ctl->pds[h]);
         }
+        ptx::mbar_arrive(&ctl->vec_free[g & 1]);
+        ptx::tmem_wait_st();
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&ctl->ds_done);
       }
     }
   }
@@ -1375,9 +1257,9 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   cudaError_t e;  // (dq_accum has been cleared by the delta pre-pass)
   void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, BwdArgs);
   if constexpr (D == 64) kern = bwd_tc64_kernel<BF16, GEN>;
-  else kern = bwd_tc_kernel<D, BF16, GEN>;
-  constexpr int kSmemBytes = D == 64 ? Cfg64::kSmem : Cfg<D>::kSmem;
-  constexpr int kBlock = D == 64 ? Cfg64::kThreads : Cfg<D>::kThreads;
+  else kern = bwd_tc_kernel<BF16, GEN>;
+  constexpr int kSmemBytes = D == 64 ? Cfg64::kSmem : Cfg128::kSmem;
+  constexpr int kBlock = D == 64 ? Cfg64::kThreads : Cfg128::kThreads;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_kt = (a.Skv + BM - 1) / BM;
