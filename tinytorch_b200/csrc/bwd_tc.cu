@@ -91,7 +91,8 @@ template <bool BF16, bool GEN>
 __global__ void __launch_bounds__(Cfg128::kThreads, 1)
     bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                  const __grid_constant__ CUtensorMap tmdQ, const BwdArgs a) {
+                  const __grid_constant__ CUtensorMap tmdQ, const __grid_constant__ CUtensorMap tmdK,
+                  const __grid_constant__ CUtensorMap tmdV, const BwdArgs a) {
   using C = Cfg128;
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   constexpr int D = C::D, TB = C::TB, HALVES = D / 64;
@@ -179,6 +180,8 @@ __global__ void __launch_bounds__(Cfg128::kThreads, 1)
     ptx::tma_prefetch_desc(&tmV);
     ptx::tma_prefetch_desc(&tmdO);
     ptx::tma_prefetch_desc(&tmdQ);
+    ptx::tma_prefetch_desc(&tmdK);
+    ptx::tma_prefetch_desc(&tmdV);
   }
   if (warp == C::kIssWarp) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -564,36 +567,44 @@ __global__ void __launch_bounds__(Cfg128::kThreads, 1)
       }
       g0 += n_steps;
 
-      // dV (warpgroup 0) and dK (warpgroup 1) of this key tile; the other warpgroups go on to the next item
+      // dV (warpgroup 0) and dK (warpgroup 1) of this key tile, 64 columns at a time through the warpgroup's
+      // staging tile and a TMA store (coalesced; rows beyond Skv are clipped by the tensor map); the other
+      // warpgroups go on to the next item
       if (wg < 2) {
-        T* out = nullptr;
-        if (wg == 0 && a.dv)
-          out = reinterpret_cast<T*>(a.dv) + b * a.dvs.b + hk * a.dvs.h + static_cast<int64_t>(kv_row) * a.dvs.s;
-        if (wg == 1 && a.dk)
-          out = reinterpret_cast<T*>(a.dk) + b * a.dks.b + hk * a.dks.h + static_cast<int64_t>(kv_row) * a.dks.s;
+        const bool wanted = wg == 0 ? a.dv != nullptr : a.dk != nullptr;
         if (ok) ok = ptx::mbar_wait(&ctl->acc_full, k & 1, abort_flag);
         ptx::tc_fence_after();
         const uint32_t src = (wg == 0 ? tdV : tdK) + lane_addr;
+        uint8_t* stage = sdq + wg * (BQ * 128);
 #pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t v[32];
-          ptx::tmem_ld32(src + cc * 32, v);
-          ptx::tmem_wait_ld();
-          if (cc == D / 32 - 1) {
-            // the accumulators may be overwritten by the next item's first products
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(&ctl->acc_free);
-          }
-          if (ok && out && kv_row < a.Skv) {
+        for (int hf = 0; hf < HALVES; ++hf) {
+          if (r == 0) ptx::bulk_wait_read();  // the previous store / reduction has read the staging tile
+          ptx::named_barrier(3 + wg, BM);
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w4;
-              w4.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-              w4.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-              w4.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-              w4.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-              *reinterpret_cast<uint4*>(out + cc * 32 + i) = w4;
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t v[32];
+            ptx::tmem_ld32(src + hf * 64 + c2 * 32, v);
+            ptx::tmem_wait_ld();
+            if (hf == HALVES - 1 && c2 == 1) {
+              // the accumulators may be overwritten by the next item's first products
+              ptx::tc_fence_before();
+              ptx::mbar_arrive(&ctl->acc_free);
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 w4;
+              w4.x = pack2<BF16>(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+              w4.y = pack2<BF16>(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+              w4.z = pack2<BF16>(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+              w4.w = pack2<BF16>(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+              *reinterpret_cast<uint4*>(stage + r * 128 + (((c2 * 4 + j) ^ (r & 7)) << 4)) = w4;
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          ptx::named_barrier(3 + wg, BM);
+          if (r == 0 && ok && wanted) {
+            ptx::tma_store_4d(wg == 0 ? &tmdV : &tmdK, stage, hf * 64, kv0, hk, b);
+            ptx::bulk_commit();
           }
         }
       }
@@ -721,7 +732,8 @@ template <bool BF16, bool GEN>
 __global__ void __launch_bounds__(Cfg64::kThreads, 1)
     bwd_tc64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const __grid_constant__ CUtensorMap tmdQ, const BwdArgs a) {
+                    const __grid_constant__ CUtensorMap tmdQ, const __grid_constant__ CUtensorMap tmdK,
+                    const __grid_constant__ CUtensorMap tmdV, const BwdArgs a) {
   using C = Cfg64;
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   constexpr int D = C::D, TB = C::TB, NQ = C::NQ;
@@ -811,6 +823,8 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
     ptx::tma_prefetch_desc(&tmV);
     ptx::tma_prefetch_desc(&tmdO);
     ptx::tma_prefetch_desc(&tmdQ);
+    ptx::tma_prefetch_desc(&tmdK);
+    ptx::tma_prefetch_desc(&tmdV);
   }
   if (warp == C::kIssWarp) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -1050,10 +1064,10 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
     // ----------------------------------------------------------------- drain --
     // Warp j of this warpgroup owns TMEM lanes [32j, 32j+32): dQ of those query rows in every step (32 columns
     // at a time through the warp's swizzled staging box and a TMA reduction: coalesced, rows beyond Lq are
-    // clipped by the tensor map), and dV / dK of those key rows (written directly) between the item's last two dQ.
+    // clipped by the tensor map), and dV / dK of those key rows (through the same box and TMA stores) between
+    // the item's last two dQ.
     ptx::setmaxnreg_dec<48>();
     const int wj = warp & 3;
-    const int r = wj * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(wj * 32) << 16;
     uint8_t* box = sdq + wj * C::kBox;
     bool ok = true;
@@ -1072,16 +1086,14 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
       const Item it = decode_item(w);
       for (int n = 0; n < it.n_steps; ++n, ++g) {
         if (n + 1 == it.n_steps) {
-          // dV, then dK: complete once the last step's products are (before its dQ)
+          // dV, then dK: complete once the last step's products are (before its dQ); through the warp's staging
+          // box (as [32 key rows][64 elements]) and a TMA store: coalesced, rows beyond Skv clipped
           wwait(&ctl->acc_full, k & 1);
           ptx::tc_fence_after();
-          const int kv_row = it.kv0 + r;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            void* base = t == 0 ? a.dv : a.dk;
-            const Str3& st = t == 0 ? a.dvs : a.dks;
-            T* out = base ? reinterpret_cast<T*>(base) + it.b * st.b + it.hk * st.h + static_cast<int64_t>(kv_row) * st.s
-                          : nullptr;
+            if (lane == 0) ptx::bulk_wait_read();  // the previous store / reduction has read the box
+            __syncwarp();
 #pragma unroll
             for (int cc = 0; cc < D / 32; ++cc) {
               uint32_t v[32];
@@ -1092,17 +1104,21 @@ __global__ void __launch_bounds__(Cfg64::kThreads, 1)
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(&ctl->acc_free);
               }
-              if (ok && out && kv_row < a.Skv) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                  uint4 w4;
-                  w4.x = pack2<BF16>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-                  w4.y = pack2<BF16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-                  w4.z = pack2<BF16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-                  w4.w = pack2<BF16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-                  *reinterpret_cast<uint4*>(out + cc * 32 + i) = w4;
-                }
+              for (int j = 0; j < 4; ++j) {
+                uint4 w4;
+                w4.x = pack2<BF16>(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+                w4.y = pack2<BF16>(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+                w4.z = pack2<BF16>(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+                w4.w = pack2<BF16>(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+                *reinterpret_cast<uint4*>(box + lane * 128 + (((cc * 4 + j) ^ (lane & 7)) << 4)) = w4;
               }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && ok && (t == 0 ? a.dv != nullptr : a.dk != nullptr) && it.kv0 + wj * 32 < a.Skv) {
+              ptx::tma_store_4d(t == 0 ? &tmdV : &tmdK, box, 0, it.kv0 + wj * 32, it.hk, it.b);
+              ptx::bulk_commit();
             }
           }
         }
@@ -1248,14 +1264,19 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const BwdArgs a) {
 template <int D, bool BF16, bool GEN>
 cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t stream) {
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-  CUtensorMap tq, tk, tv, tdo, tdq;
+  CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (!make_map(&tq, dtype, a.q, D, a.Lq, a.Hq, a.B, a.qs) || !make_map(&tk, dtype, a.k, D, a.Skv, a.Hkv, a.B, a.ks) ||
       !make_map(&tv, dtype, a.v, D, a.Skv, a.Hkv, a.B, a.vs) ||
       !make_map(&tdo, dtype, a.d_o, D, a.Lq, a.Hq, a.B, a.dos) ||
       !make_map_f32(&tdq, a.dq_accum, D, a.Lq, a.Hq, a.B, D == 64 ? 32 : 128))
     return cudaErrorInvalidValue;
+  // dK / dV leave through TMA stores (boxes of 64 columns x 32 or 128 rows); an absent output gets a map that is never used
+  constexpr int kOutRows = D == 64 ? 32 : 128;
+  if (!make_map(&tdk, dtype, a.dk ? a.dk : a.k, D, a.Skv, a.Hkv, a.B, a.dk ? a.dks : a.ks, kOutRows) ||
+      !make_map(&tdv, dtype, a.dv ? a.dv : a.v, D, a.Skv, a.Hkv, a.B, a.dv ? a.dvs : a.vs, kOutRows))
+    return cudaErrorInvalidValue;
   cudaError_t e;  // (dq_accum has been cleared by the delta pre-pass)
-  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, BwdArgs);
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, BwdArgs);
   if constexpr (D == 64) kern = bwd_tc64_kernel<BF16, GEN>;
   else kern = bwd_tc_kernel<BF16, GEN>;
   constexpr int kSmemBytes = D == 64 ? Cfg64::kSmem : Cfg128::kSmem;
@@ -1284,7 +1305,7 @@ cudaError_t launch_t(const BwdArgs& a, int dtype, int device, cudaStream_t strea
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cfg.attrs = attr, cfg.numAttrs = 1;  // early launch behind the delta pre-pass
-  e = cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tdo, tdq, ka);
+  e = cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tdo, tdq, tdk, tdv, ka);
   if (e != cudaSuccess || !a.dq) return e;
   const int64_t total = static_cast<int64_t>(a.B) * a.Hq * a.Lq * (D / 8);
   const int blocks = static_cast<int>((total + 255) / 256 < 8 * sm_count(device) ? (total + 255) / 256 : 8 * sm_count(device));

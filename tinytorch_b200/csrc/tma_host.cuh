@@ -28,16 +28,17 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [B, H, S, D] tensor, box = 64 (D) x 128 (S) x 1 x 1, 128-byte swizzle; rows
+// [B, H, S, D] tensor, box = 64 (D) x `box_rows` (S) x 1 x 1, 128-byte swizzle; rows
 // outside the tensor read as zero and are clipped on stores.
-inline bool make_map(CUtensorMap* m, int dtype, const void* ptr, int D, int S, int H, int B, const Str3& st) {
+inline bool make_map(CUtensorMap* m, int dtype, const void* ptr, int D, int S, int H, int B, const Str3& st,
+                     int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
                         static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(st.s) * 2, static_cast<cuuint64_t>(st.h) * 2,
                            static_cast<cuuint64_t>(st.b) * 2};
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(m, dtype == TT_ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
