@@ -9,10 +9,9 @@
 //   dV = P^T dO      dK = dS^T Q      dQ = dS K
 //
 // A work item is a 128-row key tile of one (batch, kv head): the CTA walks the query
-// tiles that see it (and the query heads of its group).  CTAs are persistent, one per
-// SM, and draw items from a counter; the first products of the next item are issued
-// while the last dQ of this one is computed and dV / dK are read out.  Everything is kept
-// TRANSPOSED so that a TMEM lane is a key row:
+// tiles that see it (and the query heads of its group), one 128 x 128 (key, query) pair
+// per step.  CTAs are persistent, one per SM, and draw items from a counter.  Everything is
+// kept TRANSPOSED so that a TMEM lane is a key row:
 //   S^T  = K Q^T   (SS MMA, both operands K-major)         -> TMEM region A
 //   dP^T = V dO^T  (SS MMA)                                -> TMEM region B
 //   four compute warpgroups (thread r of each = key row r; warpgroup w takes
@@ -24,12 +23,19 @@
 //   dQ   = dS K      (A = dS^T tile in shared memory read MN-major, i.e. as dS;
 //                     B = K tile read MN-major)             -> its own TMEM columns
 //                     when D = 64, else region A
-// dV and dK accumulate in TMEM over the whole walk of an item and are written once.  dQ of a
-// (key tile, query tile) pair is added to an fp32 buffer through swizzled staging
-// tiles and TMA reductions (cp.reduce.async.bulk.tensor ... add) and converted to
-// the tensor dtype by a second small kernel.  Warp 16 feeds the tiles
-// with TMA (128-byte swizzle, one copy per CTA), warp 17 runs the issuing loop with one elected lane issuing the MMAs;
+// dV and dK accumulate in TMEM over the whole walk of an item and leave once, through
+// staging tiles and TMA stores.  dQ of a (key tile, query tile) pair is added to an fp32
+// buffer through swizzled staging tiles and TMA reductions (cp.reduce.async.bulk.tensor
+// ... add) and converted to the tensor dtype by a second small kernel.  A producer warp
+// draws the items, feeds the tiles with TMA (128-byte swizzle) and fetches the per-query
+// vectors; an issuer warp runs the issuing loop with one elected lane issuing the MMAs;
 // every wait is bounded.
+//
+// Two kernels, because the 512 TMEM columns and 227 KB of shared memory divide differently:
+// D = 128 (bwd_tc_kernel) has no column to spare, so dQ shares region A with S^T and the
+// steps of an item run one after the other; D = 64 (bwd_tc64_kernel) overlaps the two
+// element-wise phases of a step with the MMAs of the neighbouring phases and gives the
+// read-out of results to a warpgroup of its own.
 #include <type_traits>
 
 #include "common.cuh"
