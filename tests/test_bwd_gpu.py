@@ -60,6 +60,47 @@ def test_bwd_shapes(oracle, dt, D, L, S, causal, Hq, Hkv):
             assert_close_16bit(to_np(got), want, dt, "%s %s D=%d L=%d S=%d" % (name, dt, D, L, S))
 
 
+@pytest.mark.parametrize("dt,D", [("f16", 64), ("bf16", 64), ("bf16", 128)])
+@pytest.mark.parametrize("causal,L,S", [(False, 640, 1536), (True, 640, 1536), ("bottom-right", 640, 1536),
+                                        (True, 1536, 1536)])
+def test_bwd_many_items_per_cta(oracle, dt, D, causal, L, S):
+    """More key tiles (4 x 4 x 12 = 192 work items) than the persistent backward kernels have CTAs, several query
+    heads per kv head, and key tiles that no query sees: whole runs of them behind short kv_lens and, under the
+    top-left causal mask with L < S, behind the last query row.  Their dK / dV must come out as zeros, the items
+    after them must still be walked, and every CTA goes through more than one item."""
+    B, Hq, Hkv = 4, 8, 4
+    q, qn = make((B, Hq, L, D), DTYPES[dt], 181)
+    k, kn = make((B, Hkv, S, D), DTYPES[dt], 182)
+    v, vn = make((B, Hkv, S, D), DTYPES[dt], 183)
+    do, don = make((B, Hq, L, D), DTYPES[dt], 184)
+    # (bottom-right: every length >= L, so that no query row is left without a key)
+    lens = np.array([S, 700, 641, S - 77] if causal == "bottom-right" else [S, 200, 1, S - 77], dtype=np.int32)
+    kw = dict(isCausal=causal, kvLens=torch.from_numpy(lens).cuda())
+    from tinytorch_b200 import op
+    o, lse = op.sdpAttentionFwd(q, k, v, **kw)
+    dq, dk, dv = op.sdpAttentionBwd(do, q, k, v, o, lse, **kw)
+    torch.cuda.synchronize()
+    okw = dict(kv_lens=lens)
+    if causal == "bottom-right":
+        # the triangle's corner sits at each sequence's own (L, kv_len)
+        bias = np.zeros((B, 1, L, S), dtype=np.float32)
+        for b in range(B):
+            i, j = np.arange(L)[:, None], np.arange(S)[None, :]
+            bias[b, 0][j > i + (int(lens[b]) - L)] = -np.inf
+        okw["bias"] = bias
+    else:
+        okw["causal"] = bool(causal)
+    wq, wk, wv = oracle.bwd(qn, kn, vn, don, **okw)
+    for name, got, want in (("dQ", dq, wq), ("dK", dk, wk), ("dV", dv, wv)):
+        g = to_np(got)
+        live = np.isfinite(want)  # (query rows without any visible key have no defined gradient in the oracle)
+        assert_close_16bit(np.where(live, g, 0.0), np.where(live, want, 0.0), dt,
+                           "%s %s D=%d causal=%s L=%d S=%d" % (name, dt, D, causal, L, S))
+    # keys beyond a sequence's length get exact zeros
+    assert float(np.abs(to_np(dk)[1, :, int(lens[1]):]).max()) == 0.0
+    assert float(np.abs(to_np(dv)[2, :, int(lens[2]):]).max()) == 0.0
+
+
 def test_config5_fp16_slices(oracle):
     # B=8 H=16 S=2048 D=64 fp16 causal fwd+bwd; oracle on two (b, h) slices
     B, H, S, D = 8, 16, 2048, 64

@@ -713,6 +713,15 @@ __device__ __forceinline__ void p_chunk(const BwdArgs& a, uint32_t (&s)[16], con
     pk[(i >> 1) + 0] = pack2<BF16>(p0, p1);
     pk[(i >> 1) + 1] = pack2<BF16>(p2, p3);
   }
+  // (the FMA-pipe exponential of -inf is a denormal, not 0: a hidden pair must leave nothing behind)
+  if (n_hidden > 7) {
+    s[7] = 0u;
+    pk[3] = pack2<BF16>(__uint_as_float(s[6]), 0.f);
+    if (n_hidden > 15) {
+      s[15] = 0u;
+      pk[7] = pack2<BF16>(__uint_as_float(s[14]), 0.f);
+    }
+  }
 }
 
 // dS = P * (scale * dP - scale * delta) of 16 queries, as packed 16-bit pairs.  p: P (fp32 bits); dp: dP^T
