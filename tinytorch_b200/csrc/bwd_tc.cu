@@ -91,6 +91,82 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+// P of 16 queries for this thread's key row: in place of s (S^T, fp32 bits) and as packed 16-bit pairs in pk.
+// lse2: -lse * log2(e) of the 16 queries; q_first: index of the first query; mo: offset of (first query, this
+// key) in the mask; n_hidden: how many of the 16 queries, from the first on, do not see this key (causal
+// triangle; all 16 for a key beyond kv_len).
+template <bool BF16, bool GEN, typename T>
+__device__ __forceinline__ void p_chunk(const BwdArgs& a, uint32_t (&s)[16], const float* lse2, float2 c2v,
+                                        int n_hidden, int kv_row, int q_first, int64_t mo, uint32_t (&pk)[8]) {
+  // exponents c*s - lse2, in packed fp32 pairs
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i);
+    float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v, make_float2(l4.x, l4.y));
+    float2 x1 =
+        ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v, make_float2(l4.z, l4.w));
+    if constexpr (GEN) {
+      if (a.mask.ptr && kv_row < a.Skv) {
+        // the mask element of (query, this thread's key): adjacent threads read adjacent keys
+        const int q = q_first + i;
+        const int64_t m = mo + static_cast<int64_t>(i) * a.mask.sl;
+        if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, m);
+        if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, m + a.mask.sl);
+        if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, m + 2 * a.mask.sl);
+        if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, m + 3 * a.mask.sl);
+      }
+    }
+    s[i] = __float_as_uint(x0.x), s[i + 1] = __float_as_uint(x0.y);
+    s[i + 2] = __float_as_uint(x1.x), s[i + 3] = __float_as_uint(x1.y);
+  }
+  // Hidden pairs get P = 0 through the exponent.  (Kept apart from the arithmetic before and after, which then
+  // is the same straight-line code for every step; only the diagonal step and a ragged last key tile come here.)
+  if (n_hidden > 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n_hidden) s[i] = 0xff800000u;  // -inf
+  }
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    // (one exponential in eight on the FMA pipe: the compute warps saturate the MUFU units in this phase)
+    const float p0 = ptx::ex2(__uint_as_float(s[i])), p1 = ptx::ex2(__uint_as_float(s[i + 1]));
+    const float p2 = ptx::ex2(__uint_as_float(s[i + 2]));
+    const float p3 = (i & 4) ? ptx::ex2_fma(__uint_as_float(s[i + 3])) : ptx::ex2(__uint_as_float(s[i + 3]));
+    s[i] = __float_as_uint(p0), s[i + 1] = __float_as_uint(p1);
+    s[i + 2] = __float_as_uint(p2), s[i + 3] = __float_as_uint(p3);
+    pk[(i >> 1) + 0] = pack2<BF16>(p0, p1);
+    pk[(i >> 1) + 1] = pack2<BF16>(p2, p3);
+  }
+  // (the FMA-pipe exponential of -inf is a denormal, not 0: a hidden pair must leave nothing behind)
+  if (n_hidden > 7) {
+    s[7] = 0u;
+    pk[3] = pack2<BF16>(__uint_as_float(s[6]), 0.f);
+    if (n_hidden > 15) {
+      s[15] = 0u;
+      pk[7] = pack2<BF16>(__uint_as_float(s[14]), 0.f);
+    }
+  }
+}
+
+// dS = P * (scale * dP - scale * delta) of 16 queries, as packed 16-bit pairs.  p: P (fp32 bits); dp: dP^T
+// (fp32 bits); dsc: -delta * scale of the 16 queries.
+template <bool BF16>
+__device__ __forceinline__ void ds_chunk(const uint32_t (&p)[16], const uint32_t (&dp)[16], const float* dsc,
+                                         float2 sc2, uint32_t (&dk)[8]) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
+    const float2 g0 =
+        ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2, make_float2(d4.x, d4.y));
+    const float2 g1 =
+        ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2, make_float2(d4.z, d4.w));
+    const float2 ds0 = ptx::mul2(make_float2(__uint_as_float(p[i]), __uint_as_float(p[i + 1])), g0);
+    const float2 ds1 = ptx::mul2(make_float2(__uint_as_float(p[i + 2]), __uint_as_float(p[i + 3])), g1);
+    dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
+    dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
+  }
+}
+
 // GEN: the general variant (a mask and / or a causal triangle that is not top-left
 // aligned); the fast variant compiles all of that out.
 template <bool BF16, bool GEN>
@@ -505,46 +581,14 @@ __global__ void __launch_bounds__(Cfg128::kThreads, 1)
           ptx::tmem_ld16(tB + lane_addr + col, dp);
           ptx::tmem_wait_ld();
           uint32_t pk[8], dk[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(vec + col + i);
-            const float4 d4 = *reinterpret_cast<const float4*>(vec + BQ + col + i);
-            // P = 2^(c*s - lse2), dS = P * (scale*dP - scale*delta), in packed fp32 pairs
-            float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v,
-                                  make_float2(l4.x, l4.y));
-            float2 x1 = ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v,
-                                  make_float2(l4.z, l4.w));
-            if constexpr (GEN) {
-              if (a.mask.ptr && kv_row < a.Skv) {
-                // the mask element of (query, this thread's key): adjacent threads read adjacent keys
-                const int q = q0 + col + i;
-                const int64_t mo = b * a.mask.sb + (hk * group + n / per_head) * a.mask.sh + q * a.mask.sl + kv_row;
-                if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, mo);
-                if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, mo + a.mask.sl);
-                if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, mo + 2 * a.mask.sl);
-                if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, mo + 3 * a.mask.sl);
-              }
-            }
-            // (one exponential in eight on the FMA pipe: the 16 compute warps saturate the MUFU units in this phase;
-            // one in four is as fast within half a percent, three in eight and more are slower again)
-            float2 p0 = make_float2(ptx::ex2(x0.x), ptx::ex2(x0.y)), p1 = make_float2(ptx::ex2(x1.x), (i & 4) ? ptx::ex2_fma(x1.y) : ptx::ex2(x1.y));
-            if (masked) {  // uniform over the CTA: only the diagonal step and a ragged last key tile
-              const int q = q0 + col + i + shift;
-              if (!row_valid || (diag && q + 0 < kv_row)) p0.x = 0.f;
-              if (!row_valid || (diag && q + 1 < kv_row)) p0.y = 0.f;
-              if (!row_valid || (diag && q + 2 < kv_row)) p1.x = 0.f;
-              if (!row_valid || (diag && q + 3 < kv_row)) p1.y = 0.f;
-            }
-            const float2 g0 = ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2,
-                                        make_float2(d4.x, d4.y));
-            const float2 g1 = ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2,
-                                        make_float2(d4.z, d4.w));
-            const float2 ds0 = ptx::mul2(p0, g0), ds1 = ptx::mul2(p1, g1);
-            pk[(i >> 1) + 0] = pack2<BF16>(p0.x, p0.y);
-            pk[(i >> 1) + 1] = pack2<BF16>(p1.x, p1.y);
-            dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
-            dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
-          }
+          int64_t mo = 0;
+          if constexpr (GEN)
+            mo = b * a.mask.sb + (hk * group + n / per_head) * a.mask.sh + static_cast<int64_t>(q0 + col) * a.mask.sl +
+                 kv_row;
+          int n_hidden = 0;
+          if (masked) n_hidden = !row_valid ? 16 : (diag ? kv_row - (q0 + col + shift) : 0);
+          p_chunk<BF16, GEN, T>(a, s, vec + col, c2v, n_hidden, kv_row, q0 + col, mo, pk);
+          ds_chunk<BF16>(s, dp, vec + BQ + col, sc2, dk);
           // Warpgroup w keeps its 16-bit results in columns [32w, 32w+16) of the
           // region, i.e. over the first 16 columns it loaded itself, never over
           // columns another warpgroup still has to read.
@@ -666,82 +710,6 @@ struct Cfg64 {
   // warps: 16 compute, 4 drain, producer, issuer, 2 idle (register reallocation works on whole warpgroups)
   static constexpr int kProdWarp = 20, kIssWarp = 21, kThreads = 768;
 };
-
-// P of 16 queries for this thread's key row: in place of s (S^T, fp32 bits) and as packed 16-bit pairs in pk.
-// lse2: -lse * log2(e) of the 16 queries; q_first: index of the first query; mo: offset of (first query, this
-// key) in the mask; n_hidden: how many of the 16 queries, from the first on, do not see this key (causal
-// triangle; all 16 for a key beyond kv_len).
-template <bool BF16, bool GEN, typename T>
-__device__ __forceinline__ void p_chunk(const BwdArgs& a, uint32_t (&s)[16], const float* lse2, float2 c2v,
-                                        int n_hidden, int kv_row, int q_first, int64_t mo, uint32_t (&pk)[8]) {
-  // exponents c*s - lse2, in packed fp32 pairs
-#pragma unroll
-  for (int i = 0; i < 16; i += 4) {
-    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + i);
-    float2 x0 = ptx::fma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), c2v, make_float2(l4.x, l4.y));
-    float2 x1 =
-        ptx::fma2(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), c2v, make_float2(l4.z, l4.w));
-    if constexpr (GEN) {
-      if (a.mask.ptr && kv_row < a.Skv) {
-        // the mask element of (query, this thread's key): adjacent threads read adjacent keys
-        const int q = q_first + i;
-        const int64_t m = mo + static_cast<int64_t>(i) * a.mask.sl;
-        if (q + 0 < a.Lq) x0.x += mask_bias2<T>(a.mask, m);
-        if (q + 1 < a.Lq) x0.y += mask_bias2<T>(a.mask, m + a.mask.sl);
-        if (q + 2 < a.Lq) x1.x += mask_bias2<T>(a.mask, m + 2 * a.mask.sl);
-        if (q + 3 < a.Lq) x1.y += mask_bias2<T>(a.mask, m + 3 * a.mask.sl);
-      }
-    }
-    s[i] = __float_as_uint(x0.x), s[i + 1] = __float_as_uint(x0.y);
-    s[i + 2] = __float_as_uint(x1.x), s[i + 3] = __float_as_uint(x1.y);
-  }
-  // Hidden pairs get P = 0 through the exponent.  (Kept apart from the arithmetic before and after, which then
-  // is the same straight-line code for every step; only the diagonal step and a ragged last key tile come here.)
-  if (n_hidden > 0) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (i < n_hidden) s[i] = 0xff800000u;  // -inf
-  }
-#pragma unroll
-  for (int i = 0; i < 16; i += 4) {
-    // (one exponential in eight on the FMA pipe: the compute warps saturate the MUFU units in this phase)
-    const float p0 = ptx::ex2(__uint_as_float(s[i])), p1 = ptx::ex2(__uint_as_float(s[i + 1]));
-    const float p2 = ptx::ex2(__uint_as_float(s[i + 2]));
-    const float p3 = (i & 4) ? ptx::ex2_fma(__uint_as_float(s[i + 3])) : ptx::ex2(__uint_as_float(s[i + 3]));
-    s[i] = __float_as_uint(p0), s[i + 1] = __float_as_uint(p1);
-    s[i + 2] = __float_as_uint(p2), s[i + 3] = __float_as_uint(p3);
-    pk[(i >> 1) + 0] = pack2<BF16>(p0, p1);
-    pk[(i >> 1) + 1] = pack2<BF16>(p2, p3);
-  }
-  // (the FMA-pipe exponential of -inf is a denormal, not 0: a hidden pair must leave nothing behind)
-  if (n_hidden > 7) {
-    s[7] = 0u;
-    pk[3] = pack2<BF16>(__uint_as_float(s[6]), 0.f);
-    if (n_hidden > 15) {
-      s[15] = 0u;
-      pk[7] = pack2<BF16>(__uint_as_float(s[14]), 0.f);
-    }
-  }
-}
-
-// dS = P * (scale * dP - scale * delta) of 16 queries, as packed 16-bit pairs.  p: P (fp32 bits); dp: dP^T
-// (fp32 bits); dsc: -delta * scale of the 16 queries.
-template <bool BF16>
-__device__ __forceinline__ void ds_chunk(const uint32_t (&p)[16], const uint32_t (&dp)[16], const float* dsc,
-                                         float2 sc2, uint32_t (&dk)[8]) {
-#pragma unroll
-  for (int i = 0; i < 16; i += 4) {
-    const float4 d4 = *reinterpret_cast<const float4*>(dsc + i);
-    const float2 g0 =
-        ptx::fma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), sc2, make_float2(d4.x, d4.y));
-    const float2 g1 =
-        ptx::fma2(make_float2(__uint_as_float(dp[i + 2]), __uint_as_float(dp[i + 3])), sc2, make_float2(d4.z, d4.w));
-    const float2 ds0 = ptx::mul2(make_float2(__uint_as_float(p[i]), __uint_as_float(p[i + 1])), g0);
-    const float2 ds1 = ptx::mul2(make_float2(__uint_as_float(p[i + 2]), __uint_as_float(p[i + 3])), g1);
-    dk[(i >> 1) + 0] = pack2<BF16>(ds0.x, ds0.y);
-    dk[(i >> 1) + 1] = pack2<BF16>(ds1.x, ds1.y);
-  }
-}
 
 template <bool BF16, bool GEN>
 __global__ void __launch_bounds__(Cfg64::kThreads, 1)
