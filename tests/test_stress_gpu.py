@@ -43,11 +43,14 @@ def _rng(seed, i):
     return np.random.default_rng([seed, i])
 
 
-def _prefill_case(rng):
+def _prefill_case(rng, big=False):
+    """big: batch x kv heads x key tiles well above the number of SMs, so that the persistent kernels' CTAs
+    walk several work items each."""
     dt = [torch.float16, torch.bfloat16][rng.integers(2)]
     D = [64, 128][rng.integers(2)]
-    B, Hkv, g = int(rng.integers(1, 4)), int(rng.integers(1, 4)), int(rng.choice([1, 2, 4]))
-    L, S = int(rng.integers(1, 1100)), int(rng.integers(1, 1100))
+    lo, hi, top = (2, 7, 1500) if big else (1, 4, 1100)
+    B, Hkv, g = int(rng.integers(lo, hi)), int(rng.integers(lo, hi)), int(rng.choice([1, 2, 4]))
+    L, S = int(rng.integers(1, top)), int(rng.integers(16 if big else 1, top))
     causal = [False, True, "bottom-right"][rng.integers(3)]
     if causal == "bottom-right" and L > S:
         L = S
@@ -92,6 +95,31 @@ def test_random_backward_cases():
             worst = max(worst, ratio)
             assert ratio <= 1.0, ("seed 12 case %d" % i, q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, ratio)
     print("random backward cases: largest error / bound = %.3f" % worst)
+
+
+def test_random_backward_cases_many_items():
+    """The same comparison on larger problems (up to 6 x 6 x 12 key tiles, 4 query heads per kv head): more work
+    items than CTAs; dK / dV must also come out bit-identical from two calls in a row (their accumulation order
+    does not depend on which CTA draws which item)."""
+    from tinytorch_b200 import op
+    worst = 0.0
+    for i in range(40):
+        q, k, v, causal, lens = _prefill_case(_rng(14, i), big=True)
+        qr, kr, vr = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+        want = _reference(qr, kr, vr, causal, lens)
+        do = torch.randn_like(want).to(q.dtype)
+        want.backward(do.float())
+        o, lse = op.sdpAttentionFwd(q, k, v, isCausal=causal, kvLens=lens)
+        assert (o.float() - want.detach()).abs().max().item() <= 2e-2, ("seed 14 case %d" % i, "forward")
+        dq, dk, dv = op.sdpAttentionBwd(do, q, k, v, o, lse, isCausal=causal, kvLens=lens)
+        _, dk2, dv2 = op.sdpAttentionBwd(do, q, k, v, o, lse, isCausal=causal, kvLens=lens)
+        assert torch.equal(dk, dk2) and torch.equal(dv, dv2), ("seed 14 case %d" % i, "dK / dV differ between calls")
+        for got, ref in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
+            bound = 2e-2 + 2.0 * ULP[q.dtype] * ref.abs() + 0.25 * ULP[q.dtype] * ref.abs().max()
+            ratio = ((got.float() - ref).abs() / bound).max().item()
+            worst = max(worst, ratio)
+            assert ratio <= 1.0, ("seed 14 case %d" % i, q.dtype, tuple(q.shape), tuple(k.shape), causal, lens, ratio)
+    print("random backward cases, many items: largest error / bound = %.3f" % worst)
 
 
 def test_random_decode_cases():
