@@ -93,7 +93,7 @@ def fwd_bytes(w):
 # processes, so the figure reported for a full launch is this ratio times the launch's algorithmic bytes.
 NCU_TRAFFIC_RATIO = {
     "fwd_tc_kernel": (254.1 / 269.5, "profiles/fwd_tc_kernel_prefill_bf16_S4096_D128.md"),
-    "bwd_tc64_kernel": (293.0 / 270.5, "profiles/bwd_tc64_kernel_train_fp16_S2048_D64.md"),
+    "bwd_tc64_kernel": (296.3 / 270.5, "profiles/bwd_tc64_kernel_train_fp16_S2048_D64.md"),
     "decode_kernel": (1218.2 / 1213.0, "profiles/decode_kernel_bf16_cap8192_D128.md"),
     "decode_tc_kernel": (1271.9 / 1248.0, "profiles/decode_tc_kernel_bf16_gqa4_cap8192_D128.md"),
     "linear_tc_kernel": (87.4 / 100.7, "profiles/linear_tc_kernel_bf16_4096x4096x4096.md"),
